@@ -1,0 +1,147 @@
+"""The C oracle against outputs of the reference's own ref_ctct.py (tests/golden/)."""
+import numpy as np
+import pytest
+
+import oracle
+
+KEYS = (("fw_simple", oracle.FW_SIMPLE), ("bw_simple", oracle.BW_SIMPLE),
+        ("fw_shift", oracle.FW_SHIFT), ("bw_shift", oracle.BW_SHIFT))
+
+
+def _cases(golden):
+    return [str(n) for n in golden["names"]]
+
+
+def test_collect_units_bit_exact(golden):
+    for name in _cases(golden):
+        lp, ys = golden[f"{name}/lp"], golden[f"{name}/ys"]
+        got = oracle.collect_units(lp[None], ys[None])[0]
+        assert np.array_equal(got, golden[f"{name}/units"]), name
+
+
+def test_tables_match_reference(golden):
+    for name in _cases(golden):
+        g3, ys = golden[f"{name}/units"], golden[f"{name}/ys"]
+        for key, which in KEYS:
+            tab, ll = oracle.table(g3, ys, which, np.float32)
+            ref = golden[f"{name}/{key}"]
+            assert tab.shape == ref.shape, (name, key)
+            # identical -inf pattern and identical untouched (debug-fill) cells
+            assert np.array_equal(np.isneginf(tab), np.isneginf(ref)), (name, key)
+            fin = np.isfinite(ref)
+            np.testing.assert_allclose(tab[fin], ref[fin], rtol=2e-6, atol=2e-6, err_msg=f"{name}/{key}")
+            np.testing.assert_allclose(ll, golden[f"{name}/{key}_ll"], rtol=2e-6, err_msg=f"{name}/{key}")
+
+
+def test_four_variants_agree_in_double(golden):
+    for name in _cases(golden):
+        g3, ys = golden[f"{name}/units"], golden[f"{name}/ys"]
+        lls = [oracle.table(g3, ys, which, np.float64)[1] for _, which in KEYS]
+        assert max(lls) - min(lls) < 1e-9 * max(1.0, abs(lls[0])), (name, lls)
+
+
+def test_demo_cost_is_the_printed_one(golden):
+    # ref_ctct.py's __main__ prints cost 3.6803 for its seed-1 example
+    assert round(-float(golden["demo/bw_shift_ll"]), 4) == 3.6803
+    g3, ys = golden["demo/units"], golden["demo/ys"]
+    assert round(-oracle.table(g3, ys, oracle.BW_SHIFT)[1], 4) == 3.6803
+
+
+def test_gradient_matches_reference_autograd(golden):
+    n_checked = 0
+    for name in _cases(golden):
+        if f"{name}/grad" not in golden:
+            continue
+        lp, ys, ref = golden[f"{name}/lp"], golden[f"{name}/ys"], golden[f"{name}/grad"]
+        T, U1, V = lp.shape
+        costs, dense = oracle.ctct_loss(lp[None], ys[None], [T], [U1 - 1])
+        np.testing.assert_allclose(costs[0], -golden[f"{name}/bw_shift_ll"], rtol=2e-6)
+        np.testing.assert_allclose(dense[0], ref, atol=5e-6, err_msg=name)
+        n_checked += 1
+    assert n_checked >= 6
+
+
+def test_one_emission_per_frame(golden):
+    # occupancies of all arcs leaving frame t sum to one
+    for name in _cases(golden):
+        lp, ys = golden[f"{name}/lp"], golden[f"{name}/ys"]
+        T, U1, V = lp.shape
+        g3 = oracle.collect_units(lp[None], ys[None])
+        _, grads = oracle.ctct_fwd(g3, ys[None], [T], [U1 - 1], True, np.float64)
+        np.testing.assert_allclose(-grads[0].sum(axis=(1, 2)), np.ones(T), atol=1e-9, err_msg=name)
+
+
+def test_finite_differences_double(golden):
+    name = "cfg1_0"
+    lp, ys = golden[f"{name}/lp"].astype(np.float32), golden[f"{name}/ys"]
+    T, U1, V = lp.shape
+    g3 = oracle.collect_units(lp[None], ys[None])
+    c0, grads = oracle.ctct_fwd(g3, ys[None], [T], [U1 - 1], True, np.float64)
+    rng = np.random.default_rng(0)
+    eps = 1e-3  # inputs are float32, so the step must be representable
+    for _ in range(20):
+        t, u, k = rng.integers(T), rng.integers(U1), rng.integers(3)
+        if (u == 0 and k == 1) or (u == U1 - 1 and k == 2):
+            continue
+        gp, gm = g3.copy(), g3.copy()
+        gp[0, t, u, k] += eps
+        gm[0, t, u, k] -= eps
+        step = float(gp[0, t, u, k]) - float(gm[0, t, u, k])
+        cp, _ = oracle.ctct_fwd(gp, ys[None], [T], [U1 - 1], False, np.float64)
+        cm, _ = oracle.ctct_fwd(gm, ys[None], [T], [U1 - 1], False, np.float64)
+        assert abs((cp[0] - cm[0]) / step - grads[0, t, u, k]) < 1e-5
+
+
+def test_collect_separate_bit_exact(golden):
+    cf, cg = oracle.collect_separate(golden["sep/f"], golden["sep/g"], golden["sep/ys"])
+    assert np.array_equal(cf, golden["sep/cf"]) and np.array_equal(cg, golden["sep/cg"])
+
+
+def test_ragged_batch_equals_per_utterance():
+    rng = np.random.default_rng(3)
+    N, T, U1, V = 5, 14, 6, 9
+    x = rng.standard_normal((N, T, U1, V)).astype(np.float32)
+    lp = x - np.log(np.exp(x).sum(-1, keepdims=True))
+    ys = rng.integers(1, V, (N, U1 - 1)).astype(np.int32)
+    lx = np.array([14, 9, 5, 11, 3], np.int32)
+    ly = np.array([5, 3, 5, 1, 2], np.int32)
+    costs, dense = oracle.ctct_loss(lp, ys, lx, ly)
+    for n in range(N):
+        c1, d1 = oracle.ctct_loss(lp[n:n + 1, :lx[n], :ly[n] + 1].copy(), ys[n:n + 1, :ly[n]].copy(), [lx[n]], [ly[n]])
+        assert costs[n] == c1[0]
+        assert np.array_equal(dense[n, :lx[n], :ly[n] + 1], d1[0])
+        assert not dense[n, lx[n]:].any() and not dense[n, :, ly[n] + 1:].any()
+
+
+def test_round_half_matches_numpy():
+    rng = np.random.default_rng(5)
+    xs = np.concatenate([rng.standard_normal(2000) * 10.0 ** rng.integers(-9, 5, 2000), [0.0, 65504.0, 65519.9, 65520.0, 1e-8, -3e-8]])
+    for x in xs.astype(np.float32):
+        with np.errstate(over="ignore"):
+            want = np.float32(np.float16(x))
+        assert oracle.round_half(float(x)) == want, x
+
+
+def test_simple_loss_equals_standard_loss_on_composed_joint():
+    rng = np.random.default_rng(9)
+    N, T, U1, V = 3, 10, 5, 12
+    f = rng.standard_normal((N, T, V)).astype(np.float32)
+    g = rng.standard_normal((N, U1, V)).astype(np.float32)
+    ys = rng.integers(1, V, (N, U1 - 1)).astype(np.int32)
+    lx, ly = np.array([10, 7, 4], np.int32), np.array([4, 2, 4], np.int32)
+    joint = f[:, :, None, :] + g[:, None, :, :]
+    lsm = joint - np.log(np.exp(joint.astype(np.float64)).sum(-1, keepdims=True))
+    c_std, d_std = oracle.ctct_loss(lsm.astype(np.float32), ys, lx, ly)
+    c_s, gf, gg = oracle.simple_loss(f, g, ys, lx, ly, normalized=True)
+    np.testing.assert_allclose(c_s, c_std, rtol=1e-5)
+    # chain rule through log_softmax: dJ = d - softmax * sum_v d
+    d = d_std.astype(np.float64)
+    dj = d - np.exp(lsm) * d.sum(-1, keepdims=True)
+    np.testing.assert_allclose(gf, dj.sum(2), atol=2e-5)
+    np.testing.assert_allclose(gg, dj.sum(1), atol=2e-5)
+    # un-normalised: the joint itself is the log-prob
+    c_u, gfu, ggu = oracle.simple_loss(f, g, ys, lx, ly, normalized=False)
+    c_j, d_j = oracle.ctct_loss(joint, ys, lx, ly)
+    np.testing.assert_allclose(c_u, c_j, rtol=1e-5)
+    np.testing.assert_allclose(gfu, d_j.astype(np.float64).sum(2), atol=2e-5)
+    np.testing.assert_allclose(ggu, d_j.astype(np.float64).sum(1), atol=2e-5)
