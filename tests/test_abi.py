@@ -1,0 +1,94 @@
+"""CPU checks of the drop-in boundary: the shared library loads, exports exactly what the header
+declares, and the Python surface mirrors the reference's signatures.  No kernel is launched."""
+import ctypes
+import inspect
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_symbols():
+    text = open(os.path.join(ROOT, "include", "ctct_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ctct_b200_\w+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def built():
+    from warp_ctct_b200 import build
+    return build.build()
+
+
+def test_header_declares_entry_points():
+    syms = _header_symbols()
+    for need in ("ctct_b200_loss_forward", "ctct_b200_loss_backward", "ctct_b200_gather",
+                 "ctct_b200_gathered_forward", "ctct_b200_workspace_bytes"):
+        assert need in syms
+
+
+def test_library_exports_every_declared_symbol(built):
+    handle = ctypes.CDLL(built)
+    for name in _header_symbols():
+        assert hasattr(handle, name), name
+
+
+def test_binding_covers_every_declared_symbol(built):
+    from warp_ctct_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == _header_symbols()
+    lib = _lib.lib()
+    assert lib.ctct_b200_abi_version() >= 1
+    assert lib.ctct_b200_strerror(0) == b"ok"
+    assert lib.ctct_b200_padded_contexts(65) == 68
+
+
+def test_workspace_and_buffer_sizes(built):
+    from warp_ctct_b200 import _lib
+    lib = _lib.lib()
+    assert lib.ctct_b200_grads3_elems(32, 256, 65) == 32 * 256 * 3 * 68
+    small = lib.ctct_b200_workspace_bytes(32, 256, 65, 0)
+    big = lib.ctct_b200_workspace_bytes(32, 256, 65, 1)
+    assert 32 * 256 * 3 * 68 * 4 <= small < big
+    assert big % 256 == 0
+    assert lib.ctct_b200_workspace_bytes(4, 16, 9000, 1) == 0  # more contexts than the kernels support
+    assert lib.ctct_b200_workspace_bytes(-1, 16, 5, 1) == 0
+
+
+def test_argument_errors_do_not_need_a_gpu(built):
+    from warp_ctct_b200 import _lib
+    lib = _lib.lib()
+    # null pointers / bad dtype are rejected before anything is launched
+    assert lib.ctct_b200_loss_forward(None, 0, None, None, None, 2, 4, 3, 5, 0, None, None, None, 0, None) == -1
+    assert lib.ctct_b200_loss_backward(None, None, None, None, None, 2, 4, 3, 5, 7, None, None) == -1
+    assert lib.ctct_b200_gather(None, 9, None, None, None, 2, 4, 3, 5, 0, None, None) == -1
+    with pytest.raises(RuntimeError):
+        _lib.check(-2, "x")
+
+
+def test_python_surface_matches_reference_signatures():
+    import warp_ctct_b200 as W
+    assert W.__all__ == ["ctct_loss", "ctct_simple_loss"]
+    p = inspect.signature(W.ctct_loss).parameters
+    assert list(p) == ["log_probs", "labels", "frames_lengths", "labels_lengths", "reduction", "average_frames"]
+    assert p["reduction"].default == "mean" and p["average_frames"].default is False
+    p = inspect.signature(W.ctct_simple_loss).parameters
+    assert list(p) == ["f", "g", "labels", "frames_lengths", "labels_lengths", "reduction", "average_frames",
+                       "normalized"]
+    assert p["normalized"].default is True
+    assert hasattr(W, "CTCTLoss")
+
+
+def test_cpu_tensors_are_rejected_like_the_reference():
+    import torch
+    import warp_ctct_b200 as W
+    lp = torch.randn(2, 4, 3, 5).log_softmax(-1)
+    ys = torch.ones(2, 2, dtype=torch.int32)
+    lens = torch.tensor([4, 4], dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="must be located in the CUDA"):
+        W.ctct_loss(lp, ys, lens, torch.tensor([2, 2], dtype=torch.int32))
+    with pytest.raises(AssertionError):
+        W.ctct_loss(lp, ys[:, :1], lens, lens)
+    with pytest.raises(AssertionError):
+        W.ctct_loss(lp, ys, lens, lens, reduction="avg")

@@ -1,0 +1,354 @@
+"""GPU parity of ctct_loss: every call goes through the C ABI of libctct_b200.so and is checked
+against the CPU oracle (oracle/, a restatement of the reference pinned to ref_ctct.py's outputs).
+
+Tolerances (from the task statement): gathers bit-exact; fp32 costs within 1e-5 relative;
+gradients within 1e-4 absolute; fp16 inputs: costs 1e-3 relative (inputs carry 11 bits),
+gradients within one fp16 ulp of the oracle's rounded value.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from util import make_case
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def W():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import warp_ctct_b200
+    from warp_ctct_b200 import _lib
+    _lib.lib()  # fails loudly if the CUDA library was not built
+    return warp_ctct_b200
+
+
+def _dev(*arrs):
+    return [torch.from_numpy(np.ascontiguousarray(a)).to(DEV) for a in arrs]
+
+
+def _gather(W, lp_t, ys_t, lx_t, ly_t, valid_only):
+    from warp_ctct_b200 import _lib
+    N, T, U1, V = lp_t.shape
+    out = torch.full((N, T, U1, 3), float("nan"), dtype=torch.float32, device=DEV)
+    rc = _lib.lib().ctct_b200_gather(lp_t.data_ptr(), _lib.dtype_code(lp_t.dtype), ys_t.data_ptr(), lx_t.data_ptr(),
+                                     ly_t.data_ptr(), N, T, U1, V, int(valid_only), out.data_ptr(),
+                                     _lib.stream_ptr(lp_t.device))
+    _lib.check(rc, "gather")
+    return out.cpu().numpy()
+
+
+# ---------------------------------------------------------------------------------- gather
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(2, 16, 5, 8), (3, 7, 4, 5), (4, 33, 17, 130), (2, 9, 66, 512)])
+def test_gather_bit_exact(W, dtype, shape):
+    N, T, U1, V = shape
+    lp, ys, lx, ly = make_case(N, T, U1, V, 1.5, seed=sum(shape), lx_range=(max(1, T // 2), T), ly_range=(1, U1 - 1))
+    lp_t = torch.from_numpy(lp).to(DEV).to(dtype)
+    ys_t, lx_t, ly_t = _dev(ys, lx, ly)
+    want = oracle.collect_units(lp_t.float().cpu().numpy(), ys)
+    got = _gather(W, lp_t, ys_t, lx_t, ly_t, valid_only=False)
+    assert np.array_equal(got, want)
+    got_v = _gather(W, lp_t, ys_t, lx_t, ly_t, valid_only=True)
+    for n in range(N):
+        assert np.array_equal(got_v[n, :lx[n], :ly[n] + 1, :2], want[n, :lx[n], :ly[n] + 1, :2])
+        assert np.array_equal(got_v[n, :lx[n], :ly[n], 2], want[n, :lx[n], :ly[n], 2])
+        assert not got_v[n, lx[n]:].any() and not got_v[n, :, ly[n] + 1:].any()
+
+
+def test_gather_ignores_garbage_padding_labels(W):
+    lp, ys, lx, ly = make_case(3, 12, 6, 9, seed=4, lx_range=(6, 12), ly_range=(1, 4))
+    ys_bad = ys.copy()
+    for n in range(3):
+        ys_bad[n, ly[n]:] = -12345  # padding a data loader might leave behind
+    lp_t, ys_t, ysb_t, lx_t, ly_t = _dev(lp, ys, ys_bad, lx, ly)
+    a = _gather(W, lp_t, ys_t, lx_t, ly_t, True)
+    b = _gather(W, lp_t, ysb_t, lx_t, ly_t, True)
+    assert np.array_equal(a, b)
+
+
+# ---------------------------------------------------------------------------------- lattice
+
+def _forward_pieces(W, lp, ys, lx, ly, want_grad=True):
+    """ctct_b200_gathered_forward + export of the tables, through the C ABI."""
+    from warp_ctct_b200 import _lib
+    lib = _lib.lib()
+    g3 = oracle.collect_units(lp, ys)
+    N, T, U1, _ = g3.shape
+    S = 2 * (U1 - 1) + 1
+    g3_t, ys_t, lx_t, ly_t = _dev(g3, ys, lx, ly)
+    costs = torch.empty(N, device=DEV)
+    grads = torch.full((N, T, U1, 3), float("nan"), device=DEV)
+    ws = _lib.workspace(N, T, U1, want_grad, torch.device(DEV))
+    st = _lib.stream_ptr(torch.device(DEV))
+    rc = lib.ctct_b200_gathered_forward(g3_t.data_ptr(), ys_t.data_ptr(), lx_t.data_ptr(), ly_t.data_ptr(), N, T, U1,
+                                        int(want_grad), costs.data_ptr(), grads.data_ptr(), ws.data_ptr(), ws.numel(), st)
+    _lib.check(rc, "gathered_forward")
+    out = {"costs": costs.cpu().numpy(), "g3": g3}
+    if want_grad:
+        alpha = torch.empty((N, T, S), dtype=torch.float64, device=DEV)
+        beta = torch.empty((N, T, S), dtype=torch.float64, device=DEV)
+        lla = torch.empty(N, dtype=torch.float64, device=DEV)
+        llb = torch.empty(N, dtype=torch.float64, device=DEV)
+        rc = lib.ctct_b200_export_tables(ws.data_ptr(), ws.numel(), lx_t.data_ptr(), ly_t.data_ptr(), N, T, U1,
+                                         alpha.data_ptr(), beta.data_ptr(), lla.data_ptr(), llb.data_ptr(), st)
+        _lib.check(rc, "export_tables")
+        out.update(grads=grads.cpu().numpy(), alpha=alpha.cpu().numpy(), beta=beta.cpu().numpy(),
+                   lla=lla.cpu().numpy(), llb=llb.cpu().numpy())
+    return out
+
+
+@pytest.mark.parametrize("shape,seed", [((2, 16, 5, 8), 1), ((5, 24, 9, 12), 2), ((3, 40, 34, 20), 3),
+                                        ((2, 70, 66, 16), 4), ((2, 150, 130, 8), 5)])
+def test_tables_match_unshifted_reference_tables(W, shape, seed):
+    N, T, U1, V = shape
+    lp, ys, lx, ly = make_case(N, T, U1, V, 1.5, seed, lx_range=(T // 2, T), ly_range=(1, U1 - 1), repeat_prob=0.15)
+    res = _forward_pieces(W, lp, ys, lx, ly)
+    for n in range(N):
+        Tn, Un = int(lx[n]), int(ly[n])
+        g3n = np.ascontiguousarray(res["g3"][n, :Tn, :Un + 1])
+        A, lla = oracle.table(g3n, ys[n], oracle.FW_SIMPLE, np.float64)
+        B, llb = oracle.table(g3n, ys[n], oracle.BW_SIMPLE, np.float64)
+        Sn = 2 * Un + 1
+        # alpha(t, s) for t < Tn; the oracle leaves cells it never visits at a debug fill, so compare
+        # only cells on a path from the start AND to the end (finite in both oracle tables)
+        got_a, got_b = res["alpha"][n, :Tn, :Sn], res["beta"][n, :Tn, :Sn]
+        live_a = np.isfinite(A[:Tn]) & np.isfinite(B[:Tn]) & (A[:Tn] != 1.0)
+        np.testing.assert_allclose(got_a[live_a], A[:Tn][live_a], atol=2e-5, rtol=0)
+        live_b = np.isfinite(B[1:Tn + 1]) & np.isfinite(A[1:Tn + 1]) & (A[1:Tn + 1] != 1.0)
+        live_b[-1] = np.isfinite(B[Tn])  # row Tn of alpha holds only the two terminal states
+        np.testing.assert_allclose(got_b[live_b], B[1:Tn + 1][live_b], atol=2e-5, rtol=0)
+        # states that cannot reach the end are impossible in the backward table
+        assert np.all(np.isneginf(got_b[np.isneginf(B[1:Tn + 1])]))
+        if np.isfinite(llb):
+            assert abs(res["lla"][n] - lla) < 1e-5 * max(1.0, abs(lla))
+            assert abs(res["llb"][n] - llb) < 1e-5 * max(1.0, abs(llb))
+        assert not np.isfinite(res["alpha"][n, Tn:]).any() and not np.isfinite(res["alpha"][n, :, Sn:]).any()
+
+
+@pytest.mark.parametrize("shape,seed,kw", [
+    ((2, 16, 5, 8), 11, {}),
+    ((6, 30, 9, 12), 12, dict(lx_range=(8, 30), ly_range=(1, 8), repeat_prob=0.3)),
+    ((4, 64, 33, 40), 13, dict(lx_range=(32, 64), ly_range=(1, 32))),
+    ((3, 50, 65, 30), 14, dict(lx_range=(50, 50), ly_range=(40, 47))),       # T close to U: narrow band
+    ((3, 90, 97, 10), 15, dict(lx_range=(60, 90), ly_range=(5, 45), repeat_prob=0.2)),
+    ((2, 140, 129, 6), 16, dict(lx_range=(100, 140), ly_range=(30, 80))),
+    ((2, 200, 161, 6), 17, dict(lx_range=(170, 200), ly_range=(80, 130))),
+    ((2, 210, 200, 6), 18, dict(lx_range=(200, 210), ly_range=(120, 160))),
+    ((2, 300, 290, 5), 19, dict(lx_range=(290, 300), ly_range=(150, 220))),   # needs two warps per direction
+    ((1, 700, 600, 4), 20, dict(lx_range=(700, 700), ly_range=(300, 400))),   # four warps
+])
+def test_costs_and_slot_gradients(W, shape, seed, kw):
+    N, T, U1, V = shape
+    lp, ys, lx, ly = make_case(N, T, U1, V, 1.5, seed, **kw)
+    res = _forward_pieces(W, lp, ys, lx, ly)
+    c32, g32 = oracle.ctct_fwd(res["g3"], ys, lx, ly, True, np.float32)
+    c64, g64 = oracle.ctct_fwd(res["g3"], ys, lx, ly, True, np.float64)
+    fin = np.isfinite(c64)
+    assert np.array_equal(np.isposinf(res["costs"]), ~fin)
+    np.testing.assert_allclose(res["costs"][fin], c32[fin], rtol=1e-5)
+    np.testing.assert_allclose(res["costs"][fin], c64[fin], rtol=2e-6)
+    g64 = np.where(fin[:, None, None, None], g64, 0.0)
+    g32 = np.where(fin[:, None, None, None], g32, 0.0)
+    # The float32 restatement of the reference accumulates its own rounding error along T (its
+    # table entries are ~ -T*log V, where one float32 ulp is ~1e-4); that error is measured as its
+    # distance to the float64 evaluation of the same formulas and added to the 1e-4 bound.  Against
+    # the float64 evaluation the kernels are held to a 5x tighter bound.
+    own32 = np.abs(g32 - g64).max()
+    assert np.abs(res["grads"] - g32).max() < 1e-4 + own32
+    assert np.abs(res["grads"] - g64).max() < 2e-5
+    # forward-only call (beta pass alone) gives the same costs
+    res2 = _forward_pieces(W, lp, ys, lx, ly, want_grad=False)
+    np.testing.assert_array_equal(res2["costs"], res["costs"])
+
+
+def test_edge_lengths(W):
+    # T == U (single path), one label, one frame, no labels at all, impossible alignments
+    N, T, U1, V = 7, 6, 5, 7
+    lp, ys, _, _ = make_case(N, T, U1, V, 1.0, 31)
+    ys[0] = [1, 2, 3, 4]
+    ys[4] = [2, 2, 3, 3]
+    lx = np.array([4, 6, 1, 6, 4, 2, 0], np.int32)
+    ly = np.array([4, 1, 1, 0, 4, 4, 0], np.int32)  # #4: repeats need 6 frames; #5: lx < ly
+    res = _forward_pieces(W, lp, ys, lx, ly)
+    g3 = res["g3"]
+    want0 = -sum(g3[0, t, t, 2] for t in range(4))
+    assert abs(res["costs"][0] - want0) < 1e-5 * abs(want0)
+    c64, g64 = oracle.ctct_fwd(g3[1:3], ys[1:3], lx[1:3], ly[1:3], True, np.float64)
+    np.testing.assert_allclose(res["costs"][1:3], c64, rtol=1e-5)
+    assert np.abs(res["grads"][1:3] - g64).max() < 2e-5
+    # no labels: the only path is all blanks (the reference leaves ly = 0 undefined)
+    assert abs(res["costs"][3] - (-g3[3, :6, 0, 0].sum())) < 1e-4
+    np.testing.assert_allclose(res["grads"][3, :6, 0, 0], -1.0, atol=1e-5)
+    assert np.isposinf(res["costs"][4]) and np.isposinf(res["costs"][5])
+    assert not res["grads"][4].any() and not res["grads"][5].any()
+    assert res["costs"][6] == 0.0 and not res["grads"][6].any()
+    assert not np.isnan(res["grads"]).any()
+
+
+def test_minus_inf_log_probs(W):
+    # -inf (probability zero) entries must act as forbidden arcs, never as NaN
+    lp, ys, lx, ly = make_case(2, 10, 4, 6, 1.0, 41)
+    lp[0, 3, :, 0] = -np.inf          # no blank at frame 3
+    lp[1, :, 1, ys[1, 0]] = -np.inf   # label 0 can never repeat
+    res = _forward_pieces(W, lp, ys, lx, ly)
+    c64, g64 = oracle.ctct_fwd(res["g3"], ys, lx, ly, True, np.float64)
+    np.testing.assert_allclose(res["costs"], c64, rtol=1e-5)
+    assert np.abs(res["grads"] - np.nan_to_num(g64)).max() < 2e-5
+
+
+# ---------------------------------------------------------------------------------- public API
+
+def _api(W, lp, ys, lx, ly, dtype=torch.float32, reduction="none", average_frames=False, grad=True, ys_dtype=torch.int32):
+    lp_t = torch.from_numpy(lp).to(DEV).to(dtype).requires_grad_(grad)
+    ys_t = torch.from_numpy(ys).to(DEV).to(ys_dtype)
+    lx_t, ly_t = _dev(lx, ly)
+    loss = W.ctct_loss(lp_t, ys_t, lx_t, ly_t, reduction=reduction, average_frames=average_frames)
+    return lp_t, loss
+
+
+def test_golden_reference_costs_and_autograd(W, golden):
+    for name in [str(n) for n in golden["names"]]:
+        lp, ys = golden[f"{name}/lp"], golden[f"{name}/ys"]
+        T, U1, V = lp.shape
+        lp_t, loss = _api(W, lp[None], ys[None], np.array([T], np.int32), np.array([U1 - 1], np.int32), reduction="sum")
+        want = -float(golden[f"{name}/bw_shift_ll"])
+        assert abs(loss.item() - want) <= 1e-5 * abs(want), name
+        if f"{name}/grad" in golden:
+            loss.backward()
+            assert np.abs(lp_t.grad[0].cpu().numpy() - golden[f"{name}/grad"]).max() < 1e-4, name
+    # first benchmark configuration: B=2, T=16, U+1=5, V=8, reduction=mean
+    lp = np.stack([golden["cfg1_0/lp"], golden["cfg1_1/lp"]])
+    ys = np.stack([golden["cfg1_0/ys"], golden["cfg1_1/ys"]])
+    _, loss = _api(W, lp, ys, np.array([16, 16], np.int32), np.array([4, 4], np.int32), reduction="mean")
+    want = -(float(golden["cfg1_0/bw_shift_ll"]) + float(golden["cfg1_1/bw_shift_ll"])) / 2
+    assert abs(loss.item() - want) <= 1e-5 * abs(want)
+
+
+@pytest.mark.parametrize("shape,seed,kw", [
+    ((3, 12, 5, 8), 51, dict(lx_range=(6, 12), ly_range=(1, 4))),
+    ((2, 20, 9, 13), 52, dict(lx_range=(10, 20), ly_range=(2, 8), repeat_prob=0.4)),   # V not a multiple of 4
+    ((4, 33, 17, 130), 53, dict(lx_range=(17, 33), ly_range=(3, 16))),                 # V % 4 == 2
+    ((2, 64, 33, 512), 54, dict(lx_range=(40, 64), ly_range=(8, 32))),
+])
+def test_dense_gradient_fp32(W, shape, seed, kw):
+    N, T, U1, V = shape
+    lp, ys, lx, ly = make_case(N, T, U1, V, 1.5, seed, **kw)
+    go = np.random.default_rng(seed).uniform(0.2, 2.0, N).astype(np.float32)
+    lp_t, loss = _api(W, lp, ys, lx, ly, ys_dtype=torch.int64)
+    loss.backward(torch.from_numpy(go).to(DEV))
+    costs, dense = oracle.ctct_loss(lp, ys, lx, ly, go)
+    np.testing.assert_allclose(loss.detach().cpu().numpy(), costs, rtol=1e-5)
+    got = lp_t.grad.cpu().numpy()
+    assert got.shape == dense.shape and got.dtype == np.float32
+    assert np.abs(got - dense).max() < 1e-4
+    for n in range(N):  # padding rows are exactly zero
+        assert not got[n, lx[n]:].any() and not got[n, :, ly[n] + 1:].any()
+        np.testing.assert_allclose(-got[n, :lx[n]].sum((1, 2)), go[n], rtol=2e-5)
+
+
+@pytest.mark.parametrize("dtype,ulp", [(torch.float16, 2.0 ** -11), (torch.bfloat16, 2.0 ** -8)])
+def test_dense_gradient_16bit(W, dtype, ulp):
+    N, T, U1, V = 3, 40, 17, 264
+    lp, ys, lx, ly = make_case(N, T, U1, V, 2.0, 61, lx_range=(20, 40), ly_range=(2, 16), repeat_prob=0.3)
+    lp16 = torch.from_numpy(lp).to(dtype)
+    lp_in = lp16.float().numpy()  # what the kernels see after the exact upcast
+    lp_t = lp16.to(DEV).requires_grad_(True)
+    ys_t, lx_t, ly_t = _dev(ys, lx, ly)
+    loss = W.ctct_loss(lp_t, ys_t, lx_t, ly_t, reduction="sum")
+    loss.backward()
+    assert lp_t.grad.dtype == dtype
+    costs, dense = oracle.ctct_loss(lp_in, ys, lx, ly)
+    assert abs(loss.item() - costs.sum()) < 1e-5 * costs.sum()
+    got = lp_t.grad.float().cpu().numpy()
+    # each value is the fp32 product rounded to 16 bits: within one unit in the last place
+    assert np.all(np.abs(got - dense) <= 2 * ulp * np.abs(dense) + 2e-5)
+    if dtype == torch.float16:
+        g3 = oracle.collect_units(lp_in, ys)
+        _, gr = oracle.ctct_fwd(g3, ys, lx, ly, True, np.float32)
+        half = oracle.scatter_dense(gr, ys, np.ones(N, np.float32), V, half_round=True)
+        assert np.abs(got - half).max() < 1e-4
+
+
+def test_reductions_average_frames_and_no_grad(W):
+    lp, ys, lx, ly = make_case(5, 18, 6, 10, 1.0, 71, lx_range=(9, 18), ly_range=(1, 5))
+    costs, _ = oracle.ctct_loss(lp, ys, lx, ly, want_grad=False)
+    for red, want in (("none", costs), (None, costs), ("sum", costs.sum()), ("mean", costs.mean())):
+        _, loss = _api(W, lp, ys, lx, ly, reduction=red, grad=False)
+        np.testing.assert_allclose(loss.cpu().numpy(), want, rtol=1e-5)
+        assert not loss.requires_grad
+    _, loss = _api(W, lp, ys, lx, ly, reduction="mean", average_frames=True)
+    np.testing.assert_allclose(loss.item(), (costs / lx).mean(), rtol=1e-5)
+    # gradient of the mean of per-frame-averaged costs: scale 1 / (N * lx[n])
+    lp_t, loss = _api(W, lp, ys, lx, ly, reduction="mean", average_frames=True)
+    loss.backward()
+    _, dense = oracle.ctct_loss(lp, ys, lx, ly, (1.0 / (5 * lx)).astype(np.float32))
+    assert np.abs(lp_t.grad.cpu().numpy() - dense).max() < 1e-5
+    with torch.no_grad():
+        lp_t, loss = _api(W, lp, ys, lx, ly, reduction="sum")
+        assert not loss.requires_grad
+    # double and non-contiguous inputs are accepted like any tensor torch.gather takes
+    lp_t = torch.from_numpy(lp).to(DEV).double().requires_grad_(True)
+    ys_t, lx_t, ly_t = _dev(ys, lx, ly)
+    W.ctct_loss(lp_t, ys_t, lx_t, ly_t, reduction="sum").backward()
+    assert lp_t.grad.dtype == torch.float64
+    lp_nc = torch.from_numpy(lp).to(DEV).transpose(1, 2).contiguous().transpose(1, 2).requires_grad_(True)
+    W.ctct_loss(lp_nc, ys_t, lx_t, ly_t, reduction="sum").backward()
+    _, dense = oracle.ctct_loss(lp, ys, lx, ly)
+    assert np.abs(lp_nc.grad.cpu().numpy() - dense).max() < 1e-4
+
+
+def test_extension_level_entry_point_and_compat_class(W):
+    lp, ys, lx, ly = make_case(3, 14, 6, 9, 1.0, 81, lx_range=(7, 14), ly_range=(1, 5))
+    g3 = oracle.collect_units(lp, ys)
+    g3_t, ys_t, lx_t, ly_t = _dev(g3, ys, lx, ly)
+    costs, grads = W.ctct_loss_fwd(g3_t, ys_t, lx_t, ly_t, True)
+    c32, g32 = oracle.ctct_fwd(g3, ys, lx, ly)
+    np.testing.assert_allclose(costs.cpu().numpy(), c32, rtol=1e-5)
+    assert np.abs(grads.cpu().numpy() - g32).max() < 1e-4
+    c2, g2 = W.ctct_loss_fwd(g3_t, ys_t, lx_t, ly_t, False)
+    assert c2 is g2
+    with pytest.raises(RuntimeError, match="Float tensor"):
+        W.ctct_loss_fwd(g3_t.half(), ys_t, lx_t, ly_t, True)
+    with pytest.raises(RuntimeError, match="Int tensor"):
+        W.ctct_loss_fwd(g3_t, ys_t.long(), lx_t, ly_t, True)
+    with pytest.raises(RuntimeError, match="length 3"):
+        W.ctct_loss_fwd(g3_t[..., :2].contiguous(), ys_t, lx_t, ly_t, True)
+    x = g3_t.clone().requires_grad_(True)
+    W.CTCTLoss.apply(x, ys_t, lx_t, ly_t, True).sum().backward()
+    assert np.abs(x.grad.cpu().numpy() - g32).max() < 1e-4
+
+
+# ---------------------------------------------------------------------------------- full-size properties
+
+def test_benchmark_shape_properties(W):
+    """B=32, T=256, U+1=65, V=512 fp32: too large for the oracle end to end, so check what does not
+    depend on size: one emission per frame, zero padding, alpha/beta agreement, and a sample of
+    utterances against the oracle."""
+    N, T, U1, V = 32, 256, 65, 512
+    g = torch.Generator(device=DEV).manual_seed(2000)
+    lp_t = (1.5 * torch.randn((N, T, U1, V), device=DEV, generator=g)).log_softmax(-1).requires_grad_(True)
+    rng = np.random.default_rng(2000)
+    lx = rng.integers(128, 257, N).astype(np.int32)
+    ly = np.minimum(rng.integers(16, 65, N), lx // 2).astype(np.int32)
+    ys = rng.integers(1, V, (N, U1 - 1)).astype(np.int32)
+    ys_t, lx_t, ly_t = _dev(ys, lx, ly)
+    costs = W.ctct_loss(lp_t, ys_t, lx_t, ly_t, reduction="none")
+    costs.sum().backward()
+    grad = lp_t.grad
+    per_frame = -grad.sum((2, 3)).cpu().numpy()
+    for n in range(N):
+        np.testing.assert_allclose(per_frame[n, :lx[n]], 1.0, atol=2e-5)
+        assert not per_frame[n, lx[n]:].any()
+        assert not grad[n, :, ly[n] + 1:].any().item()
+    assert (grad != 0).sum().item() <= 3 * int((lx * (ly + 1)).sum())
+    for n in (0, 7, 31):
+        lp_n = lp_t[n:n + 1].detach().cpu().numpy()
+        c, d = oracle.ctct_loss(lp_n, ys[n:n + 1], lx[n:n + 1], ly[n:n + 1])
+        assert abs(costs[n].item() - c[0]) <= 1e-5 * c[0]
+        assert np.abs(grad[n].cpu().numpy() - d[0]).max() < 1e-4

@@ -1,0 +1,193 @@
+"""B200-native CTC-Transducer loss with the Python surface of maxwellzh/warp-ctct.
+
+``ctct_loss`` and ``ctct_simple_loss`` keep the reference's signatures, assertions, reductions,
+blank index (0) and autograd behaviour (warp_ctct/__init__.py:88-236).  Underneath, every step
+runs in hand-written sm_100a CUDA kernels reached through the C ABI of ``libctct_b200.so``
+(``include/ctct_b200.h``); there is no PyTorch, Triton or CPU fallback.
+
+blank = 0
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+__version__ = "0.3.0"  # the reference release whose API this mirrors (setup.py:18)
+__all__ = ["ctct_loss", "ctct_simple_loss"]
+
+T = torch.Tensor
+
+
+def _require_cuda(**tensors) -> None:
+    # csrc/binding.cpp:14-16,44-49: every tensor argument must live on the GPU
+    for name, t in tensors.items():
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be located in the CUDA")
+
+
+def _as_int(t: T) -> T:
+    return t.to(torch.int32).contiguous()
+
+
+class FusedCTCTLoss(torch.autograd.Function):
+    """costs = CTC-T loss of the FULL joint tensor (N,T,U+1,V); gather, lattice and the
+    occupancy gradient are fused behind one C-ABI call, the dense gradient behind another.
+
+    Replaces the chain gather -> .float() -> CTCTLoss of warp_ctct/__init__.py:124-136."""
+
+    @staticmethod
+    def forward(ctx, log_probs: T, labels: T, lx: T, ly: T, requires_grad: bool):
+        N, Tm, U1, V = log_probs.shape
+        dev = log_probs.device
+        lib = _lib.lib()
+        costs = torch.empty((N,), dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            ws = _lib.workspace(N, Tm, U1, requires_grad, dev)
+            grads3 = None
+            if requires_grad:
+                grads3 = torch.empty((lib.ctct_b200_grads3_elems(N, Tm, U1),), dtype=torch.float32, device=dev)
+            rc = lib.ctct_b200_loss_forward(
+                _lib.ptr(log_probs), _lib.dtype_code(log_probs.dtype), _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
+                N, Tm, U1, V, int(requires_grad), _lib.ptr(costs), _lib.ptr(grads3), _lib.ptr(ws), ws.numel(),
+                _lib.stream_ptr(dev))
+        _lib.check(rc, "ctct_b200_loss_forward")
+        if requires_grad:
+            ctx.save_for_backward(grads3, labels, lx, ly)
+            ctx.meta = (N, Tm, U1, V, log_probs.dtype)
+        return costs
+
+    @staticmethod
+    def backward(ctx, grad_outputs: T):
+        grads3, labels, lx, ly = ctx.saved_tensors
+        N, Tm, U1, V, dtype = ctx.meta
+        dev = grads3.device
+        go = grad_outputs.to(torch.float32).contiguous()
+        dense = torch.empty((N, Tm, U1, V), dtype=dtype, device=dev)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().ctct_b200_loss_backward(
+                _lib.ptr(grads3), _lib.ptr(go), _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
+                N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
+        _lib.check(rc, "ctct_b200_loss_backward")
+        return dense, None, None, None, None
+
+
+def ctct_loss_fwd(log_probs: T, ys: T, lx: T, ly: T, requires_grad: bool):
+    """Extension-level entry point of the reference, ``_C.ctct_loss_fwd`` (csrc/binding.cpp:31-100):
+    gathered float32 log-probs (N,T,U+1,3) -> (costs, grads); ``grads`` is ``costs`` when no
+    gradient is requested.  Same checks, same error type."""
+    for name, t in (("log_probs", log_probs), ("ys", ys), ("lx", lx), ("ly", ly)):
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    if log_probs.dtype != torch.float32:
+        raise RuntimeError("log_probs must be a Float tensor")
+    for name, t in (("ys", ys), ("lx", lx), ("ly", ly)):
+        if t.dtype != torch.int32:
+            raise RuntimeError(f"{name} must be a Int tensor")
+    _require_cuda(log_probs=log_probs, ys=ys, lx=lx, ly=ly)
+    if log_probs.dim() != 4:
+        raise RuntimeError("log probs must have 4 dims.")
+    if log_probs.size(3) != 3:
+        raise RuntimeError("log probs should be first gathered to length 3 at last dim.")
+    if ys.dim() != 2:
+        raise RuntimeError("targets must have 2 dims.")
+    if lx.dim() != 1:
+        raise RuntimeError("lx must have only 1 dim.")
+    if ly.dim() != 1:
+        raise RuntimeError("ly must have only 1 dim.")
+    if not (log_probs.size(0) == ys.size(0) == lx.size(0) == ly.size(0)):
+        raise RuntimeError("input args should match at dim 0 (batch N)")
+    N, Tm, U1, _ = log_probs.shape
+    dev = log_probs.device
+    costs = torch.empty((N,), dtype=torch.float32, device=dev)
+    grads = torch.empty_like(log_probs) if requires_grad else None
+    with torch.cuda.device(dev):
+        ws = _lib.workspace(N, Tm, U1, requires_grad, dev)
+        rc = _lib.lib().ctct_b200_gathered_forward(
+            _lib.ptr(log_probs), _lib.ptr(ys), _lib.ptr(lx), _lib.ptr(ly), N, Tm, U1, int(requires_grad),
+            _lib.ptr(costs), _lib.ptr(grads), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+    _lib.check(rc, "ctct_b200_gathered_forward")
+    return (costs, grads) if requires_grad else (costs, costs)
+
+
+class CTCTLoss(torch.autograd.Function):
+    """Same contract as the reference class (warp_ctct/__init__.py:20-33): the input is the
+    gathered (N,T,U+1,3) float32 tensor and the gradient has that shape."""
+
+    @staticmethod
+    def forward(ctx, log_probs: T, labels: T, lx: T, ly: T, requires_grad: bool):
+        costs, grads = ctct_loss_fwd(log_probs, labels, lx, ly, requires_grad)
+        if requires_grad:
+            ctx.save_for_backward(grads)
+        return costs
+
+    @staticmethod
+    def backward(ctx, grad_outputs: T):
+        (grads,) = ctx.saved_tensors
+        return grad_outputs.view(-1, 1, 1, 1) * grads, None, None, None, None
+
+
+def _reduce(costs: T, frames_lengths: T, reduction, average_frames) -> T:
+    # warp_ctct/__init__.py:138-147
+    if average_frames:
+        costs = costs / frames_lengths
+    if reduction == "none" or reduction is None:
+        return costs
+    elif reduction == "sum":
+        return costs.sum()
+    elif reduction == "mean":
+        return costs.mean()
+    return costs
+
+
+def ctct_loss(log_probs: torch.FloatTensor,
+              labels: torch.IntTensor,
+              frames_lengths: torch.IntTensor,
+              labels_lengths: torch.IntTensor,
+              reduction: Optional[str] = "mean",
+              average_frames: bool = False) -> torch.Tensor:
+    """The CTC-Transducer loss (drop-in for ``warp_ctct.ctct_loss``, warp_ctct/__init__.py:88-147).
+
+    Args:
+        log_probs: (N, T, U, V) log-probabilities; N batch, T frames, U = max labels + 1,
+            V vocabulary including the blank at index 0.  float32, float16 or bfloat16
+            (accumulation is float32); other floating types are converted to float32.
+        labels: (N, U-1) integer labels.
+        frames_lengths: (N,) number of frames per utterance.
+        labels_lengths: (N,) number of labels per utterance.
+        reduction: 'none' | 'mean' | 'sum' | None.
+        average_frames: divide each utterance's loss by its number of frames.
+    """
+    assert average_frames is None or isinstance(average_frames, bool)
+    assert reduction is None or reduction in ("none", "mean", "sum")
+
+    assert log_probs.dim() == 4
+    assert labels.dim() == 2
+    assert log_probs.size(2) == labels.size(1) + 1
+    assert log_probs.size(0) == labels.size(0) == frames_lengths.size(0) == labels_lengths.size(0)
+
+    _require_cuda(log_probs=log_probs, ys=labels, lx=frames_lengths, ly=labels_lengths)
+    enable_grad = log_probs.requires_grad and torch.is_grad_enabled()
+    if log_probs.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        log_probs = log_probs.float()
+    if not log_probs.is_contiguous():
+        log_probs = log_probs.contiguous()
+    costs = FusedCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
+                                enable_grad)
+    return _reduce(costs, frames_lengths, reduction, average_frames)
+
+
+def ctct_simple_loss(f: torch.FloatTensor,
+                     g: torch.FloatTensor,
+                     labels: torch.IntTensor,
+                     frames_lengths: torch.IntTensor,
+                     labels_lengths: torch.IntTensor,
+                     reduction: Optional[str] = "mean",
+                     average_frames: bool = False,
+                     normalized: bool = True) -> torch.Tensor:
+    """The CTC-Transducer loss with the log-add joiner (warp_ctct/__init__.py:150-236)."""
+    from .simple import ctct_simple_loss as _impl
+
+    return _impl(f, g, labels, frames_lengths, labels_lengths, reduction, average_frames, normalized)
