@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""Benchmark of the CTC-Transducer loss hot path (fwd + bwd of ctct_loss) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload c2|c3|c5]
+
+One "step" is one forward + backward of ``ctct_loss`` over one batch of synthetic utterances per
+GPU.  Default workload (``c2``): float32 log-probs = log_softmax(1.5 * N(0,1)), B=32 per GPU,
+T=256, U+1=65, V=512, frame lengths U[128,256], label lengths U[16,64] capped at frames/2.
+With N > 1 (launched by torchrun, one rank per GPU) a global batch of 32*N utterances is
+split length-balanced over the ranks; the only collective is the scalar-loss all-reduce.
+
+Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU restatement of the
+reference's algorithm (oracle/) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B per GPU, T, U+1, V, dtype, sigma, lx range, ly range, cap ly at lx//2)
+    "c2": (32, 256, 65, 512, "f32", 1.5, (128, 256), (16, 64), True),
+    "c3": (16, 512, 129, 1024, "f16", 2.0, (256, 512), (32, 128), False),
+    "c5": (32, 400, 101, 1024, "f16", 2.0, (100, 400), (10, 100), True),
+}
+METRIC = "utterances/sec fwd+bwd"
+UNIT = "utt/s"
+
+# DRAM bytes (read + write) of one dense-gradient launch at the c2 workload, from the ncu capture
+# summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until captured.
+NCU_TRAFFIC_PER_LAUNCH = {"c2": None}
+
+
+def workload_string(name, n_gpus):
+    B, T, U1, V, dt, sigma, lxr, lyr, cap = WORKLOADS[name]
+    return (f"{name}: ctct_loss {dt} fwd+bwd, B={B}/GPU (global {B * n_gpus}), T={T}, U+1={U1}, V={V}, "
+            f"log_softmax({sigma}*N(0,1)), lx~U{list(lxr)}, ly~U{list(lyr)}" + (" capped lx//2" if cap else ""))
+
+
+def global_lengths(name, n_gpus, seed=2000):
+    B, T, U1, V, dt, sigma, lxr, lyr, cap = WORKLOADS[name]
+    rng = np.random.default_rng(seed)
+    G = B * n_gpus
+    lx = rng.integers(lxr[0], lxr[1] + 1, G).astype(np.int32)
+    ly = rng.integers(lyr[0], lyr[1] + 1, G).astype(np.int32)
+    if cap:
+        ly = np.minimum(ly, lx // 2).astype(np.int32)
+    ly = np.minimum(ly, lx).astype(np.int32)
+    ys = rng.integers(1, V, (G, U1 - 1)).astype(np.int32)
+    return lx, ly, ys
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, device_index: int, period_s: float = 0.01):
+        super().__init__(daemon=True)
+        self.period, self.samples, self.reasons, self.stop_flag = period_s, [], set(), threading.Event()
+        self.max_mhz, self.ok = None, False
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.nv = pynvml
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def sample(self):
+        nv = self.nv
+        self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+        mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)) if hasattr(
+            nv, "nvmlDeviceGetCurrentClocksEventReasons") else int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+                 0x80: "hw_power_brake_slowdown"}
+        for bit, name in names.items():
+            if mask & bit:
+                self.reasons.add(name)
+
+    def run(self):
+        if not self.ok:
+            return
+        while not self.stop_flag.is_set():
+            try:
+                self.sample()
+            except Exception:
+                break
+            time.sleep(self.period)
+
+    def finish(self):
+        self.stop_flag.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------------------- reference arm
+
+def run_reference(args):
+    """CPU arm: the C restatement of the reference's algorithm (oracle/) on all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    import oracle
+    B, T, U1, V, dt, sigma, lxr, lyr, cap = WORKLOADS[args.workload]
+    lx, ly, ys = global_lengths(args.workload, 1)
+    rng = np.random.default_rng(2000)
+    x = sigma * rng.standard_normal((B, T, U1, V), dtype=np.float32)
+    x -= x.max(-1, keepdims=True)
+    lp = x - np.log(np.exp(x).sum(-1, keepdims=True))
+    if dt == "f16":
+        lp = lp.astype(np.float16).astype(np.float32)
+    go = np.full((B,), 1.0 / B, np.float32)
+    cores = oracle.max_threads()
+    for _ in range(args.warmup):
+        oracle.ctct_loss(lp, ys, lx, ly, go, nthreads=cores)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.ctct_loss(lp, ys, lx, ly, go, nthreads=cores)
+    dt_s = time.perf_counter() - t0
+    value = B * args.steps / dt_s
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt_s / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dt, "data": "synthetic",
+        "config": {"workload": workload_string(args.workload, 1)},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"every step = the full batch of {B} utterances on {cores} OpenMP threads"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# --------------------------------------------------------------------------------------- B200 arm
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    import warp_ctct_b200 as W
+    from warp_ctct_b200 import _lib
+    from warp_ctct_b200.sharded import plan_shards, sharded_ctct_loss, shard_weights
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+        args.gpus = world
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the CTC-T kernels have no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.lib()
+
+    B, T, U1, V, dt, sigma, lxr, lyr, cap = WORKLOADS[args.workload]
+    tdt = {"f32": torch.float32, "f16": torch.float16}[dt]
+    esize = {"f32": 4, "f16": 2}[dt]
+    lx_g, ly_g, ys_g = global_lengths(args.workload, world)
+    plan = plan_shards(lx_g, ly_g, world)
+    mine = np.array(plan[rank])
+    lx, ly, ys = lx_g[mine], ly_g[mine], ys_g[mine]
+    assert len(mine) == B
+
+    gen = torch.Generator(device=dev).manual_seed(2000 + rank)
+    lp = (sigma * torch.randn((B, T, U1, V), device=dev, generator=gen)).log_softmax(-1).to(tdt)
+    lp.requires_grad_(True)
+    ys_t = torch.from_numpy(ys).to(dev)
+    lx_t = torch.from_numpy(lx).to(dev)
+    ly_t = torch.from_numpy(ly).to(dev)
+    G = B * world
+
+    def step():
+        lp.grad = None
+        loss = sharded_ctct_loss(lp, ys_t, lx_t, ly_t, global_batch=G, reduction="mean")
+        loss.backward()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    _lib.check(lib.ctct_b200_profile_enable(2 * args.steps + 2), "profile_enable")
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.start()
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        loss = step()
+    ev1.record()
+    barrier()
+    clocks = sampler.finish() if sampler else None
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+
+    # per-kernel durations recorded by the library during the timed region
+    cap_n = 2 * args.steps + 2
+    buf = np.zeros((cap_n, 4), np.float32)
+    kinds = np.zeros((cap_n,), np.int32)
+    n_rec = lib.ctct_b200_profile_read(buf.ctypes.data, kinds.ctypes.data, cap_n)
+    lib.ctct_b200_profile_disable()
+    fwd = buf[:n_rec][kinds[:n_rec] == 0]
+    bwd = buf[:n_rec][kinds[:n_rec] == 1]
+    k_ms = {"gather": float(fwd[:, 0].mean()), "lattice": float(fwd[:, 1].mean()),
+            "fill_grad": float(fwd[:, 2].mean()), "dense_grad": float(bwd[:, 0].mean())}
+
+    value = G * args.steps / (ms_total * 1e-3)
+    peak, peak_kind = peaks()
+    rows_valid = int((lx.astype(np.int64) * (ly + 1)).sum())
+    dense_bytes = B * T * U1 * V * esize + rows_valid * 16  # written once + compact gradient records read
+    gather_bytes = rows_valid * 3 * 32 + B * T * U1 * 16    # one 32-byte sector per picked element + records out
+    ach = dense_bytes / (k_ms["dense_grad"] * 1e-3) / 1e9
+    roofline = {"kernel": "k_dense_grad (dense gradient streamer)", "bound": "hbm", "achieved": ach, "peak": peak,
+                "unit": "GB/s", "frac": ach / peak, "peak_source": f"of {peak_kind}",
+                "algorithmic_bytes": dense_bytes, "traffic": NCU_TRAFFIC_PER_LAUNCH.get(args.workload)}
+    g_ach = gather_bytes / (k_ms["gather"] * 1e-3) / 1e9
+    kernels = {
+        "gather": {"ms": k_ms["gather"], "sector_bytes": gather_bytes, "GB/s": g_ach, "frac": g_ach / peak},
+        "lattice": {"ms": k_ms["lattice"], "ns_per_row": 1e6 * k_ms["lattice"] / max(int(lx.max()), 1),
+                    "note": "alpha and beta CTAs of all utterances run concurrently; rows = longest utterance"},
+        "fill_grad": {"ms": k_ms["fill_grad"]},
+        "dense_grad": {"ms": k_ms["dense_grad"], "GB/s": ach, "frac": ach / peak},
+        "sum_ms": sum(k_ms.values()),
+    }
+
+    # ---- end to end through the public API, inputs in pinned host memory ----
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    lp_host = torch.empty((B, T, U1, V), dtype=tdt, pin_memory=True)
+    lp_host.copy_(lp.detach())
+    ys_h, lx_h, ly_h = ys_t.cpu().pin_memory(), lx_t.cpu().pin_memory(), ly_t.cpu().pin_memory()
+    del lp
+    torch.cuda.empty_cache()
+
+    def e2e_step():
+        x = lp_host.to(dev, non_blocking=True).requires_grad_(True)
+        y, a, b = ys_h.to(dev, non_blocking=True), lx_h.to(dev, non_blocking=True), ly_h.to(dev, non_blocking=True)
+        loss = sharded_ctct_loss(x, y, a, b, global_batch=G, reduction="mean")
+        loss.backward()
+        return float(loss.item())  # device -> host read of the step's result
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    ev0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    ev1.record()
+    barrier()
+    ms_e = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms_e, op=dist.ReduceOp.MAX)
+    e2e_value = G * e2e_steps / (float(ms_e.item()) * 1e-3)
+    h2d = lp_host.numel() * esize + ys_h.numel() * 4 + lx_h.numel() * 4 + ly_h.numel() * 4
+    e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d * world), "d2h_bytes_per_step": 4 * world,
+           "steps": e2e_steps, "note": "joint tensor copied from pinned host memory every step; the dense gradient "
+                                       "stays on the device, the loss scalar is read back"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": dt, "data": "synthetic",
+        "config": {"workload": workload_string(args.workload, world),
+                   "l2": f"inputs larger than L2: {B * T * U1 * V * esize / 1e9:.2f} GB joint tensor read sparsely and "
+                         f"an equally large gradient written every step (L2 is 126 MB)",
+                   "shard_weights": shard_weights(lx_g, ly_g, plan)},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps * world,
+        "roofline": roofline, "kernels": kernels,
+    }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle
+        cores = oracle.max_threads()
+        lp_np = lp_host.float().numpy()
+        go = np.full((B,), 1.0 / B, np.float32)
+        oracle.ctct_loss(lp_np, ys, lx, ly, go, nthreads=cores)
+        reps, t0 = 3, time.perf_counter()
+        for _ in range(reps):
+            costs_cpu, _ = oracle.ctct_loss(lp_np, ys, lx, ly, go, nthreads=cores)
+        dt_s = (time.perf_counter() - t0) / reps
+        line["cpu_baseline"] = {"value": B / dt_s, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"the full batch of {B} utterances, mean of {reps} passes, "
+                                          f"{cores} OpenMP threads; loss agrees with the GPU to "
+                                          f"{abs(float(costs_cpu.mean()) - float(loss.item())) / float(costs_cpu.mean()):.1e} rel"}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--e2e-steps", type=int, default=20)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps == 200 and "--steps" not in " ".join(sys.argv):
+            args.steps, args.warmup = 10, 3
+        return run_reference(args)
+    return run_b200(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

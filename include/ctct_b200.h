@@ -36,12 +36,10 @@ extern "C" {
 int ctct_b200_abi_version(void);
 const char *ctct_b200_strerror(int code);
 
-/* Number of floats per (utterance, frame) row group of the internal 3-slot layout:
- * contexts padded to a multiple of 4 so that every row starts on 16 bytes. */
-int64_t ctct_b200_padded_contexts(int64_t U1);
-
 /* Elements (floats) of the compact gradient buffer `grads3` used between
- * ctct_b200_loss_forward and ctct_b200_loss_backward: N*T*3*padded_contexts(U1). */
+ * ctct_b200_loss_forward and ctct_b200_loss_backward: one 16-byte record
+ * {blank, repeat-label, next-label, 0} per (n,t,u), i.e. N*T*U1*4 floats; the buffer
+ * must be 16-byte aligned. */
 size_t ctct_b200_grads3_elems(int64_t N, int64_t T, int64_t U1);
 
 /* Bytes of scratch the forward entry points need (256-byte aligned base). */
@@ -56,7 +54,7 @@ size_t ctct_b200_workspace_bytes(int64_t N, int64_t T, int64_t U1, int want_grad
  *   costs (N) float32 out: -log-likelihood (the reference's -betas[:,0,0]); +inf when
  *         the utterance has no alignment (lx < ly + adjacent repeats)
  *   grads3 out, only if want_grad: occupancy gradient w.r.t. the three gathered
- *         log-probs per (n,t,u) in the internal layout [n][t][slot][padded u]
+ *         log-probs per (n,t,u), one 16-byte record {g0,g1,g2,0} each
  * Labels are only dereferenced for u < ly[n]; frames t >= lx[n] and contexts
  * u > ly[n] of log_probs are never read.
  */
@@ -114,12 +112,64 @@ int ctct_b200_export_tables(const void *workspace, size_t workspace_bytes, const
                             const int32_t *ly, int64_t N, int64_t T, int64_t U1, double *alpha,
                             double *beta_next, double *ll_alpha, double *ll_beta, void *stream);
 
+/* ------------------------------------------------------------------------- *
+ * log-add joiner ("simple" loss)
+ * ------------------------------------------------------------------------- */
+
+/*
+ * Batched log-semiring matrix product out[b,i,j] = log sum_k exp(lhs[b,i,k] + rhs[b,k,j]),
+ * float32, element strides given explicitly (the reference passes rhs as the transposed
+ * view g.transpose(1,2), warp_ctct/__init__.py:195-200); out is (B,M,N) contiguous.
+ * Replaces log_matmul of csrc/binding.cpp:224-245 / log_matmul_cuda_impl of csrc/core.h:39-41
+ * (kernel csrc/logmatmul.cu:44-181).  Exact for any dynamic range; all -inf gives -inf.
+ */
+int ctct_b200_log_matmul(const float *lhs, int64_t lhs_stride_b, int64_t lhs_stride_i, int64_t lhs_stride_k,
+                         const float *rhs, int64_t rhs_stride_b, int64_t rhs_stride_k, int64_t rhs_stride_j,
+                         int64_t B, int64_t M, int64_t K, int64_t N, float *out, void *stream);
+
+/*
+ * Backward of the product above for an arbitrary (signed) grad_out (B,M,N):
+ *   grad_lhs[b,i,k]  = sum_j grad_out[b,i,j] * exp(lhs[b,i,k] + rhs[b,k,j] - res[b,i,j])
+ *   grad_rhsT[b,j,k] = sum_i (same term)
+ * Replaces log_matmul_backward of csrc/binding.cpp:247-324.  lhs (B,M,K), rhsT = rhs transposed
+ * (B,N,K), res (B,M,N), all contiguous; either output may be NULL.
+ */
+int ctct_b200_log_matmul_backward(const float *grad_out, const float *lhs, const float *rhsT, const float *res,
+                                  int64_t B, int64_t M, int64_t K, int64_t N, float *grad_lhs, float *grad_rhsT,
+                                  void *stream);
+
+/*
+ * Fused forward of ctct_simple_loss after the denominator: gathers of f and g, composition of
+ * f + g - den, lattice and occupancy gradient.  Replaces the two torch.gather calls of
+ * warp_ctct/__init__.py:204-215 and ctct_loss_simple_fwd of csrc/binding.cpp:103-222 (launchers
+ * run_warp_ctct_simple / run_fill_grad_simple, csrc/core.h:22-37; kernels csrc/simple.cu,
+ * csrc/simple_unnorm.cu).
+ *   f (N,T,V), g (N,U1,V) float32 contiguous; den (N,T,U1) or NULL for the un-normalised loss
+ *   costs, grads3, workspace: as for ctct_b200_loss_forward (same workspace size).
+ */
+int ctct_b200_simple_forward(const float *f, const float *g, const float *den, const int32_t *ys,
+                             const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
+                             int want_grad, float *costs, float *grads3, void *workspace,
+                             size_t workspace_bytes, void *stream);
+
+/*
+ * Dense gradients of ctct_simple_loss w.r.t. f (N,T,V) and g (N,U1,V), each written once:
+ * the lattice's sparse part (reductions of csrc/binding.cpp:198,209-219 and the backward of the
+ * two gathers) plus, when den is given, the part that flows through the denominator
+ * (log_matmul_backward, csrc/binding.cpp:247-324), all scaled by grad_out[n]
+ * (SimpleCTCTLoss.backward, warp_ctct/__init__.py:76-85).  Either output may be NULL.
+ */
+int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const float *f, const float *g,
+                              const float *den, const int32_t *ys, const int32_t *lx, const int32_t *ly,
+                              int64_t N, int64_t T, int64_t U1, int64_t V, float *grad_f, float *grad_g,
+                              void *stream);
+
 /*
  * Optional per-kernel timing for benchmarks (no counterpart in the reference).  While
  * enabled, every ctct_b200_loss_forward records CUDA events on its stream before the gather,
  * after the gather, after the lattice and after the occupancy-gradient kernel, and every
  * ctct_b200_loss_backward records one before and one after the dense-gradient kernel.
- * Events are created once by _enable (room for max_calls calls, per calling thread) and
+ * Events are created once by _enable (room for max_calls calls, shared by all host threads) and
  * destroyed by _disable; nothing is recorded when profiling is off.
  *   ctct_b200_profile_read: waits for the recorded events, writes for call i
  *     kind[i] (0 forward, 1 backward) and ms[4*i .. 4*i+2] = {gather, lattice, fill_grad}

@@ -1,0 +1,203 @@
+"""GPU parity of the log-add joiner loss (ctct_simple_loss), of the log-semiring matmul and of
+the reference's auxiliary classes; every call goes through the C ABI and is checked against the
+CPU oracle.  Tolerances: costs 1e-5 relative, gradients 1e-4 absolute (the oracle evaluates the
+denominator's backward in float64)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def W():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import warp_ctct_b200
+    from warp_ctct_b200 import _lib
+    _lib.lib()
+    return warp_ctct_b200
+
+
+def _dev(*arrs):
+    return [torch.from_numpy(np.ascontiguousarray(a)).to(DEV) for a in arrs]
+
+
+def _case(N, T, U1, V, seed, lx_range, ly_range, scale=1.0, repeat_prob=0.0):
+    rng = np.random.default_rng(seed)
+    f = (scale * rng.standard_normal((N, T, V))).astype(np.float32)
+    g = (scale * rng.standard_normal((N, U1, V))).astype(np.float32)
+    ys = rng.integers(1, V, (N, U1 - 1)).astype(np.int32)
+    for n in range(N):
+        for u in range(1, U1 - 1):
+            if rng.random() < repeat_prob:
+                ys[n, u] = ys[n, u - 1]
+    lx = rng.integers(lx_range[0], lx_range[1] + 1, N).astype(np.int32)
+    ly = np.minimum(rng.integers(ly_range[0], ly_range[1] + 1, N), lx).astype(np.int32)
+    lx[0] = T
+    return f, g, ys, lx, ly
+
+
+# ------------------------------------------------------------------------------ log_matmul
+
+@pytest.mark.parametrize("B,M,N,K", [(2, 7, 5, 9), (3, 33, 17, 130), (2, 64, 101, 513), (1, 50, 40, 4096)])
+def test_log_matmul_matches_oracle(W, B, M, N, K):
+    from warp_ctct_b200.simple import log_matmul
+    rng = np.random.default_rng(B * 1000 + K)
+    f = (2.0 * rng.standard_normal((B, M, K))).astype(np.float32)
+    g = (2.0 * rng.standard_normal((B, N, K))).astype(np.float32)
+    want = oracle.log_matmul(f, g, np.float64)
+    f_t, g_t = _dev(f, g)
+    got = log_matmul(f_t, g_t.transpose(1, 2))                 # the strided view the reference passes
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=0, atol=2e-5)
+    got2 = log_matmul(f_t, g_t.transpose(1, 2).contiguous())   # plain (B,K,N) layout
+    np.testing.assert_allclose(got2.cpu().numpy(), want, rtol=0, atol=2e-5)
+
+
+def test_log_matmul_extreme_values(W):
+    from warp_ctct_b200.simple import log_matmul
+    rng = np.random.default_rng(5)
+    f = (30.0 * rng.standard_normal((2, 9, 40))).astype(np.float32)   # ~ +-100 nats of range per row
+    g = (30.0 * rng.standard_normal((2, 6, 40))).astype(np.float32)
+    f[0, 0, :] = -np.inf                       # a row of zeros in probability space
+    f[1, 2, :20] = -np.inf
+    g[0, 1, 3] = 5000.0                        # exp overflows float32, the log-space result must not
+    want = oracle.log_matmul(f, g, np.float64)
+    got = log_matmul(*[t for t in (_dev(f)[0], _dev(g)[0].transpose(1, 2))]).cpu().numpy()
+    assert np.all(np.isneginf(got[0, 0])) and np.all(np.isneginf(want[0, 0]))
+    fin = np.isfinite(want)
+    np.testing.assert_allclose(got[fin], want[fin], rtol=2e-6, atol=2e-5)
+    with pytest.raises(RuntimeError, match="Float tensor"):
+        log_matmul(_dev(f)[0].half(), _dev(g)[0].transpose(1, 2))
+    with pytest.raises(RuntimeError, match="invalid sizes"):
+        log_matmul(_dev(f)[0], _dev(g)[0])
+
+
+def test_log_matmul_backward_signed_grad(W):
+    from warp_ctct_b200.simple import log_matmul, log_matmul_backward
+    rng = np.random.default_rng(8)
+    B, M, N, K = 2, 20, 9, 70
+    f = rng.standard_normal((B, M, K)).astype(np.float32)
+    g = rng.standard_normal((B, N, K)).astype(np.float32)
+    go = rng.standard_normal((B, M, N)).astype(np.float32)    # both signs, as a standalone op may see
+    f_t, g_t, go_t = _dev(f, g, go)
+    rhs = g_t.transpose(1, 2)
+    res = log_matmul(f_t, rhs)
+    gl, gr = log_matmul_backward(go_t, f_t, rhs, res, [True, True])
+    assert gl.shape == (B, M, K) and gr.shape == (B, K, N)
+    wl, wr = oracle.log_matmul_backward(go, f, g, res.cpu().numpy())
+    np.testing.assert_allclose(gl.cpu().numpy(), wl, atol=2e-5)
+    np.testing.assert_allclose(gr.transpose(1, 2).cpu().numpy(), wr, atol=2e-5)
+    gl2, gr2 = log_matmul_backward(go_t, f_t, rhs, res, [False, True])
+    assert gl2 is None and torch.equal(gr2, gr)
+    assert log_matmul_backward(None, f_t, rhs, res, [True, True]) == (None, None)
+
+
+def test_logmmexp_autograd_matches_logsumexp(W):
+    rng = np.random.default_rng(9)
+    f = torch.from_numpy(rng.standard_normal((2, 11, 30)).astype(np.float32)).to(DEV)
+    g = torch.from_numpy(rng.standard_normal((2, 6, 30)).astype(np.float32)).to(DEV)
+    w = torch.from_numpy(rng.standard_normal((2, 11, 6)).astype(np.float32)).to(DEV)
+    a, b = f.clone().requires_grad_(True), g.clone().requires_grad_(True)
+    (W.LogMMExp.apply(a, b.transpose(1, 2), True, True) * w).sum().backward()
+    c, d = f.double().requires_grad_(True), g.double().requires_grad_(True)
+    (torch.logsumexp(c[:, :, None, :] + d[:, None, :, :], -1) * w.double()).sum().backward()
+    np.testing.assert_allclose(a.grad.cpu().numpy(), c.grad.cpu().numpy(), atol=2e-5)
+    np.testing.assert_allclose(b.grad.cpu().numpy(), d.grad.cpu().numpy(), atol=2e-5)
+
+
+# ------------------------------------------------------------------------------ the loss
+
+@pytest.mark.parametrize("shape,seed,kw", [
+    ((2, 10, 5, 12), 1, dict(lx_range=(6, 10), ly_range=(1, 4))),
+    ((4, 25, 9, 40), 2, dict(lx_range=(12, 25), ly_range=(2, 8), repeat_prob=0.3)),
+    ((3, 40, 17, 130), 3, dict(lx_range=(20, 40), ly_range=(4, 16))),
+    ((2, 30, 34, 67), 4, dict(lx_range=(30, 30), ly_range=(20, 28))),
+    ((2, 60, 21, 4096), 5, dict(lx_range=(30, 60), ly_range=(5, 20))),   # vocabulary of the benchmark config
+])
+@pytest.mark.parametrize("normalized", [True, False])
+def test_simple_loss_costs_and_gradients(W, shape, seed, kw, normalized):
+    N, T, U1, V = shape
+    f, g, ys, lx, ly = _case(N, T, U1, V, seed, **kw)
+    go = np.random.default_rng(seed).uniform(0.3, 1.5, N).astype(np.float32)
+    f_t, g_t = [t.requires_grad_(True) for t in _dev(f, g)]
+    ys_t, lx_t, ly_t, go_t = _dev(ys, lx, ly, go)
+    costs = W.ctct_simple_loss(f_t, g_t, ys_t, lx_t, ly_t, reduction="none", normalized=normalized)
+    costs.backward(go_t)
+    c_ref, gf_ref, gg_ref = oracle.simple_loss(f, g, ys, lx, ly, normalized, go)
+    fin = np.isfinite(c_ref)
+    assert fin.all()
+    np.testing.assert_allclose(costs.detach().cpu().numpy(), c_ref, rtol=1e-5)
+    # entries of grad_f / grad_g are sums of up to T*(U+1) occupancies (|value| up to ~T), so the
+    # 1e-4 absolute bound on a single occupancy becomes 1e-4 + 2e-5 relative on the sums
+    np.testing.assert_allclose(f_t.grad.cpu().numpy(), gf_ref, atol=1e-4, rtol=2e-5)
+    np.testing.assert_allclose(g_t.grad.cpu().numpy(), gg_ref, atol=1e-4, rtol=2e-5)
+    for n in range(N):   # nothing flows into padding frames / contexts
+        assert not f_t.grad[n, lx[n]:].any().item() and not g_t.grad[n, ly[n] + 1:].any().item()
+
+
+def test_simple_loss_equals_standard_loss_on_the_joint(W):
+    N, T, U1, V = 3, 22, 8, 50
+    f, g, ys, lx, ly = _case(N, T, U1, V, 11, (10, 22), (2, 7))
+    f_t, g_t, ys_t, lx_t, ly_t = _dev(f, g, ys, lx, ly)
+    a, b = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    W.ctct_simple_loss(a, b, ys_t, lx_t, ly_t, reduction="mean", average_frames=True).backward()
+    c, d = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    joint = (c[:, :, None, :] + d[:, None, :, :]).log_softmax(-1)
+    W.ctct_loss(joint, ys_t, lx_t, ly_t, reduction="mean", average_frames=True).backward()
+    assert (a.grad - c.grad).abs().max().item() < 2e-5 and (b.grad - d.grad).abs().max().item() < 2e-5
+    # un-normalised: the raw sum is the log-prob
+    a2, b2 = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    l1 = W.ctct_simple_loss(a2, b2, ys_t, lx_t, ly_t, reduction="sum", normalized=False)
+    c2, d2 = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    l2 = W.ctct_loss(c2[:, :, None, :] + d2[:, None, :, :], ys_t, lx_t, ly_t, reduction="sum")
+    l1.backward()
+    l2.backward()
+    assert abs(l1.item() - l2.item()) < 1e-5 * abs(l2.item())
+    assert (a2.grad - c2.grad).abs().max().item() < 2e-5 and (b2.grad - d2.grad).abs().max().item() < 2e-5
+
+
+def test_simple_loss_tracks_only_what_requires_grad(W):
+    N, T, U1, V = 2, 12, 5, 20
+    f, g, ys, lx, ly = _case(N, T, U1, V, 13, (8, 12), (1, 4))
+    f_t, g_t, ys_t, lx_t, ly_t = _dev(f, g, ys, lx, ly)
+    a = f_t.clone().requires_grad_(True)
+    loss = W.ctct_simple_loss(a, g_t, ys_t, lx_t, ly_t)
+    loss.backward()
+    assert a.grad is not None and g_t.grad is None
+    with torch.no_grad():
+        l0 = W.ctct_simple_loss(a, g_t, ys_t, lx_t, ly_t)
+    assert not l0.requires_grad and abs(l0.item() - loss.item()) < 1e-6 * abs(loss.item())
+    # half inputs are up-cast like the reference does with .float()
+    l16 = W.ctct_simple_loss(f_t.half(), g_t.half(), ys_t, lx_t, ly_t)
+    c_ref, _, _ = oracle.simple_loss(f_t.half().float().cpu().numpy(), g_t.half().float().cpu().numpy(), ys, lx, ly)
+    assert abs(l16.item() - c_ref.mean()) < 1e-5 * c_ref.mean()
+
+
+def test_reference_style_simple_class(W):
+    """SimpleCTCTLoss with pre-gathered f, g and den, as the reference wires it up
+    (warp_ctct/__init__.py:195-225), against the fused path."""
+    N, T, U1, V = 3, 14, 6, 18
+    f, g, ys, lx, ly = _case(N, T, U1, V, 17, (7, 14), (1, 5), repeat_prob=0.2)
+    f_t, g_t, ys_t, lx_t, ly_t = _dev(f, g, ys, lx, ly)
+    a, b = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    den = W.LogMMExp.apply(a, b.transpose(1, 2), True, True)
+    idx = torch.zeros((N, T, U1), dtype=torch.long, device=DEV)
+    idx[..., 1:] = ys_t.long().unsqueeze(1).expand(-1, T, -1)
+    cf = a.gather(-1, idx)
+    idg = torch.zeros((N, U1, 3), dtype=torch.long, device=DEV)
+    idg[:, 1:, 1] = ys_t.long()
+    idg[:, :U1 - 1, 2] = ys_t.long()
+    cg = b.gather(-1, idg)
+    cf_np, cg_np = oracle.collect_separate(f, g, ys)
+    assert np.array_equal(cf.detach().cpu().numpy(), cf_np) and np.array_equal(cg.detach().cpu().numpy(), cg_np)
+    costs = W.SimpleCTCTLoss.apply(cf, cg, den, ys_t, lx_t, ly_t, True, True)
+    costs.sum().backward()
+    c, d = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    fused = W.ctct_simple_loss(c, d, ys_t, lx_t, ly_t, reduction="none")
+    fused.sum().backward()
+    np.testing.assert_allclose(costs.detach().cpu().numpy(), fused.detach().cpu().numpy(), rtol=1e-5)
+    assert (a.grad - c.grad).abs().max().item() < 5e-5 and (b.grad - d.grad).abs().max().item() < 5e-5

@@ -179,6 +179,10 @@ def ctct_loss(log_probs: torch.FloatTensor,
     return _reduce(costs, frames_lengths, reduction, average_frames)
 
 
+from .simple import (FusedSimpleCTCTLoss, LogMMExp, SimpleCTCTLoss, ctct_loss_simple_fwd,  # noqa: E402,F401
+                     log_matmul, log_matmul_backward)
+
+
 def ctct_simple_loss(f: torch.FloatTensor,
                      g: torch.FloatTensor,
                      labels: torch.IntTensor,

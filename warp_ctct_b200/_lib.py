@@ -24,7 +24,6 @@ _vp, _i64, _int, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_size_t
 SIGNATURES = {
     "ctct_b200_abi_version": (_int, []),
     "ctct_b200_strerror": (C.c_char_p, [_int]),
-    "ctct_b200_padded_contexts": (_i64, [_i64]),
     "ctct_b200_grads3_elems": (_sz, [_i64, _i64, _i64]),
     "ctct_b200_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "ctct_b200_loss_forward": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
@@ -32,6 +31,10 @@ SIGNATURES = {
     "ctct_b200_gather": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "ctct_b200_gathered_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
     "ctct_b200_export_tables": (_int, [_vp, _sz, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "ctct_b200_log_matmul": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "ctct_b200_log_matmul_backward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
+    "ctct_b200_simple_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
+    "ctct_b200_simple_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
     "ctct_b200_profile_enable": (_int, [_int]),
     "ctct_b200_profile_read": (_int, [_vp, _vp, _int]),
     "ctct_b200_profile_disable": (_int, []),

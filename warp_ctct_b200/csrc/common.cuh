@@ -34,6 +34,12 @@ __device__ __forceinline__ float lse2(float a, float b) {
     return m + lg2(1.0f + ex2(n - m));
 }
 
+// log2(2^a + 2^b + 2^c) for finite a, b, c.
+__device__ __forceinline__ float lse3(float a, float b, float c) {
+    const float m = fmaxf(a, fmaxf(b, c));
+    return m + lg2(ex2(a - m) + ex2(b - m) + ex2(c - m));
+}
+
 // natural-log input value -> clamped log2 value
 __device__ __forceinline__ float to_log2(float lp) { return fmaxf(lp * LOG2E, NEG); }
 

@@ -3,11 +3,13 @@
 #include "../../include/ctct_b200.h"
 
 #include <cstdio>
+#include <mutex>
 
 #include "common.cuh"
 #include "gather.cuh"
 #include "grad.cuh"
 #include "lattice.cuh"
+#include "simple.cuh"
 
 using namespace ctct;
 
@@ -28,10 +30,14 @@ struct Profiler {
     int *kind = nullptr;
     int cap = 0, used = 0;
 };
-thread_local Profiler g_prof;
+// process-wide: autograd runs the backward call on a different host thread than the forward
+Profiler g_prof;
+std::mutex g_prof_mutex;
 
 // returns the 4 events of the next call slot, or nullptr when profiling is off / full
 cudaEvent_t *prof_slot(int kind) {
+    if (!g_prof.ev) return nullptr;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
     if (!g_prof.ev || g_prof.used >= g_prof.cap) return nullptr;
     g_prof.kind[g_prof.used] = kind;
     return g_prof.ev + 4 * (g_prof.used++);
@@ -46,48 +52,35 @@ int sm_count() {
     return sms > 0 ? sms : 148;
 }
 
-// contexts per lane (C) and warps per direction (W) for a given number of contexts
+// contexts per thread (C) and threads per CTA for a given number of contexts: one context per
+// thread up to 1024 contexts, then 2, 4 or 8 per thread
 struct LatCfg {
-    int C, W, NL;
+    int C, threads;
 };
 bool lattice_config(int64_t U1, LatCfg *cfg) {
     if (U1 < 1 || U1 > 8192) return false;
-    int C, W = 1;
-    if (U1 <= 32) C = 1;
-    else if (U1 <= 64) C = 2;
-    else if (U1 <= 96) C = 3;
-    else if (U1 <= 128) C = 4;
-    else if (U1 <= 160) C = 5;
-    else if (U1 <= 192) C = 6;
-    else {
-        C = 8;
-        const int need = static_cast<int>((U1 + 255) / 256);
-        while (W < need) W *= 2;
-    }
+    int C = 1;
+    while (U1 > 1024 * C) C *= 2;
+    const int lanes = static_cast<int>((U1 + C - 1) / C);
     cfg->C = C;
-    cfg->W = W;
-    cfg->NL = static_cast<int>(pad4((U1 + C - 1) / C));
+    cfg->threads = ((lanes + 31) / 32) * 32;
     return true;
 }
 
 size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 struct WsLayout {
-    size_t G, TAB, OFF, LLF, LLI, total;
-    int U1p;
+    size_t G, TAB, LLF, LLI, total;
     LatCfg cfg;
 };
 bool ws_layout(int64_t N, int64_t T, int64_t U1, int want_grad, WsLayout *w) {
     if (!lattice_config(U1, &w->cfg)) return false;
-    w->U1p = static_cast<int>(pad4(U1));
-    const size_t rows = static_cast<size_t>(N) * static_cast<size_t>(T);
+    const size_t recs = static_cast<size_t>(N) * static_cast<size_t>(T) * static_cast<size_t>(U1);
     size_t o = 0;
     w->G = o;
-    o = align256(o + rows * 3 * w->U1p * sizeof(float));
+    o = align256(o + recs * sizeof(float4));
     w->TAB = o;
-    if (want_grad) o = align256(o + rows * 4 * w->U1p * sizeof(float));
-    w->OFF = o;
-    if (want_grad) o = align256(o + rows * 2 * w->cfg.NL * sizeof(int));
+    if (want_grad) o = align256(o + recs * 2 * sizeof(float4));
     w->LLF = o;
     o = align256(o + static_cast<size_t>(N) * 2 * sizeof(float));
     w->LLI = o;
@@ -97,43 +90,43 @@ bool ws_layout(int64_t N, int64_t T, int64_t U1, int want_grad, WsLayout *w) {
 }
 
 bool dims_ok(int64_t N, int64_t T, int64_t U1) {
-    return N >= 0 && T >= 0 && U1 >= 1 && N <= 65535 && T * U1 < (int64_t(1) << 31) &&
-           N * T * 3 * pad4(U1) < (int64_t(1) << 40);
+    return N >= 0 && T >= 0 && U1 >= 1 && N <= 65535 && T * U1 < (int64_t(1) << 31) && N * T < (int64_t(1) << 31) &&
+           N * T * U1 < (int64_t(1) << 38);
 }
 
-template <int C, int W>
-int launch_lattice_inst(const LatticeArgs &a, int N, size_t smem, cudaStream_t st) {
+template <int C>
+int launch_lattice_inst(const LatticeArgs &a, int N, int threads, size_t smem, cudaStream_t st) {
     if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(k_lattice<C, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(k_lattice<C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem)) != cudaSuccess)
             return check_launch("lattice smem attribute");
     }
     dim3 grid(N, a.beta_only ? 1 : 2);
-    k_lattice<C, W><<<grid, W * 32, smem, st>>>(a);
+    k_lattice<C><<<grid, threads, smem, st>>>(a);
     return check_launch("lattice");
 }
 
 int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st) {
     if (N == 0) return CTCT_OK;
-    const size_t rowbytes = static_cast<size_t>(3) * a.U1p * sizeof(float);
+    const size_t rowbytes = static_cast<size_t>(a.U1) * sizeof(float4);
     int F = static_cast<int>((48 * 1024) / rowbytes);
     F = F < 1 ? 1 : (F > 16 ? 16 : F);
     a.F = F;
-    const size_t smem = 2 * static_cast<size_t>(F) * rowbytes + 4 * cfg.W * sizeof(float);
+    const size_t smem = 2 * static_cast<size_t>(F) * rowbytes + 2 * 32 * sizeof(float4);
     if (smem > 220 * 1024) return CTCT_ERR_UNSUPPORTED;
-#define LAT(Cv, Wv) \
-    if (cfg.C == Cv && cfg.W == Wv) return launch_lattice_inst<Cv, Wv>(a, N, smem, st);
-    LAT(1, 1) LAT(2, 1) LAT(3, 1) LAT(4, 1) LAT(5, 1) LAT(6, 1) LAT(8, 1)
-    LAT(8, 2) LAT(8, 4) LAT(8, 8) LAT(8, 16) LAT(8, 32)
-#undef LAT
+    switch (cfg.C) {
+    case 1: return launch_lattice_inst<1>(a, N, cfg.threads, smem, st);
+    case 2: return launch_lattice_inst<2>(a, N, cfg.threads, smem, st);
+    case 4: return launch_lattice_inst<4>(a, N, cfg.threads, smem, st);
+    case 8: return launch_lattice_inst<8>(a, N, cfg.threads, smem, st);
+    }
     return CTCT_ERR_UNSUPPORTED;
 }
 
 template <typename InT>
 int launch_gather_t(const void *lp, const int *ys, const int *lx, const int *ly, float *out, int64_t N,
                     int64_t T, int64_t U1, int64_t V, bool internal, int valid_only, cudaStream_t st) {
-    const int U1p = static_cast<int>(pad4(U1));
-    const int64_t total = internal ? N * T * 3 * U1p : N * T * U1 * 3;
+    const int64_t total = internal ? N * T * U1 * 4 : N * T * U1 * 3;
     if (total == 0) return CTCT_OK;
     const int64_t want = (total + 256 * 4 - 1) / (256 * 4);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
@@ -142,14 +135,14 @@ int launch_gather_t(const void *lp, const int *ys, const int *lx, const int *ly,
     const bool small = total < (int64_t(1) << 31) - int64_t(grid) * 256 * 4;
     if (internal) {
         if (small)
-            k_gather3<InT, unsigned, true><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, U1p, (int)V, (unsigned)total, valid_only);
+            k_gather3<InT, unsigned, true><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only);
         else
-            k_gather3<InT, unsigned long long, true><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, U1p, (int)V, (unsigned long long)total, valid_only);
+            k_gather3<InT, unsigned long long, true><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only);
     } else {
         if (small)
-            k_gather3<InT, unsigned, false><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, U1p, (int)V, (unsigned)total, valid_only);
+            k_gather3<InT, unsigned, false><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only);
         else
-            k_gather3<InT, unsigned long long, false><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, U1p, (int)V, (unsigned long long)total, valid_only);
+            k_gather3<InT, unsigned long long, false><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only);
     }
     return check_launch("gather");
 }
@@ -168,9 +161,8 @@ int launch_fill_grad(const WsLayout &w, char *ws, const int *ys, const int *lx, 
                      int ref_layout, int64_t N, int64_t T, int64_t U1, cudaStream_t st) {
     if (N == 0 || T == 0) return CTCT_OK;
     GradArgs g;
-    g.G = reinterpret_cast<const float *>(ws + w.G);
-    g.TAB = reinterpret_cast<const float *>(ws + w.TAB);
-    g.OFF = reinterpret_cast<const int *>(ws + w.OFF);
+    g.G = reinterpret_cast<const float4 *>(ws + w.G);
+    g.TAB = reinterpret_cast<const float4 *>(ws + w.TAB);
     g.llf = reinterpret_cast<const float *>(ws + w.LLF);
     g.lli = reinterpret_cast<const int *>(ws + w.LLI);
     g.ys = ys;
@@ -179,9 +171,6 @@ int launch_fill_grad(const WsLayout &w, char *ws, const int *ys, const int *lx, 
     g.out = out;
     g.T = (int)T;
     g.U1 = (int)U1;
-    g.U1p = w.U1p;
-    g.NL = w.cfg.NL;
-    g.C = w.cfg.C;
     g.ref_layout = ref_layout;
     const int cells = static_cast<int>(T * U1);
     dim3 grid((cells + 255) / 256, (unsigned)N);
@@ -192,37 +181,70 @@ int launch_fill_grad(const WsLayout &w, char *ws, const int *ys, const int *lx, 
 LatticeArgs make_lattice_args(const WsLayout &w, char *ws, const int *ys, const int *lx, const int *ly,
                               float *costs, int64_t T, int64_t U1, int want_grad) {
     LatticeArgs a;
-    a.G = reinterpret_cast<const float *>(ws + w.G);
+    a.G = reinterpret_cast<const float4 *>(ws + w.G);
     a.ys = ys;
     a.lx = lx;
     a.ly = ly;
-    a.TAB = reinterpret_cast<float *>(ws + w.TAB);
-    a.OFF = reinterpret_cast<int *>(ws + w.OFF);
+    a.TAB = reinterpret_cast<float4 *>(ws + w.TAB);
     a.llf = reinterpret_cast<float *>(ws + w.LLF);
     a.lli = reinterpret_cast<int *>(ws + w.LLI);
     a.costs = costs;
     a.T = (int)T;
     a.U1 = (int)U1;
-    a.U1p = w.U1p;
-    a.NL = w.cfg.NL;
     a.F = 1;
     a.beta_only = want_grad ? 0 : 1;
     return a;
 }
 
 template <typename OutT>
-int launch_scatter_t(const ScatterArgs &a, cudaStream_t st) {
-    if (a.rows == 0 || a.V == 0) return CTCT_OK;
+int launch_dense_t(DenseArgs a, int64_t N, cudaStream_t st) {
+    const int64_t slabs = N * a.T;
+    if (slabs == 0 || a.V == 0) return CTCT_OK;
     constexpr int E = OutOps<OutT>::E;
-    const bool vec = (a.V % E == 0) && (reinterpret_cast<uintptr_t>(a.out) % 16 == 0);
-    const int64_t want = (a.rows + 7) / 8;
-    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
-    const int grid = static_cast<int>(want < cap ? want : cap);
-    if (vec)
-        k_scatter_dense<OutT, true><<<grid, 256, 0, st>>>(a);
-    else
-        k_scatter_dense<OutT, false><<<grid, 256, 0, st>>>(a);
-    return check_launch("scatter_dense");
+    a.vec = (a.V % E == 0) && (reinterpret_cast<uintptr_t>(a.out) % 16 == 0);
+    k_dense_grad<OutT><<<static_cast<unsigned>(slabs), 256, 0, st>>>(a);
+    return check_launch("dense_grad");
+}
+
+int launch_logmm(const float *lhs, int64_t lsb, int64_t lsi, int64_t lsk, const float *rhs, int64_t rsb, int64_t rsk,
+                 int64_t rsj, int64_t B, int64_t M, int64_t K, int64_t N, float *out, cudaStream_t st) {
+    if (B == 0 || M == 0 || N == 0) return CTCT_OK;
+    LogmmArgs a;
+    a.lhs = lhs;
+    a.rhs = rhs;
+    a.out = out;
+    a.lsb = lsb;
+    a.lsi = lsi;
+    a.lsk = lsk;
+    a.rsb = rsb;
+    a.rsk = rsk;
+    a.rsj = rsj;
+    a.M = (int)M;
+    a.K = (int)K;
+    a.N = (int)N;
+    dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 31) / 32), (unsigned)B);
+    k_logmm_exact<<<grid, 256, 0, st>>>(a);
+    return check_launch("log_matmul");
+}
+
+template <int VT>
+int launch_logmm_bwd_inst(const LogmmBwdArgs &a, int64_t B, size_t smem, cudaStream_t st) {
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(k_logmm_bwd_exact<VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return check_launch("log_matmul_backward smem attribute");
+    dim3 grid((unsigned)((a.K + VT - 1) / VT), (unsigned)B);
+    k_logmm_bwd_exact<VT><<<grid, VT, smem, st>>>(a);
+    return check_launch("log_matmul_backward");
+}
+
+int launch_logmm_bwd(const LogmmBwdArgs &a, int64_t B, cudaStream_t st) {
+    if (B == 0 || a.K == 0) return CTCT_OK;
+    const size_t limit = 200 * 1024;
+    auto need = [&](int vt) { return (2 * static_cast<size_t>(a.Nc) * vt + 2 * static_cast<size_t>(a.Nc)) * sizeof(float); };
+    if (need(128) <= limit) return launch_logmm_bwd_inst<128>(a, B, need(128), st);
+    if (need(64) <= limit) return launch_logmm_bwd_inst<64>(a, B, need(64), st);
+    if (need(32) <= limit) return launch_logmm_bwd_inst<32>(a, B, need(32), st);
+    return CTCT_ERR_UNSUPPORTED;
 }
 
 }  // namespace
@@ -242,11 +264,9 @@ const char *ctct_b200_strerror(int code) {
     return "unknown error";
 }
 
-int64_t ctct_b200_padded_contexts(int64_t U1) { return pad4(U1); }
-
 size_t ctct_b200_grads3_elems(int64_t N, int64_t T, int64_t U1) {
     if (N < 0 || T < 0 || U1 < 1) return 0;
-    return static_cast<size_t>(N) * T * 3 * pad4(U1);
+    return static_cast<size_t>(N) * T * U1 * 4;
 }
 
 size_t ctct_b200_workspace_bytes(int64_t N, int64_t T, int64_t U1, int want_grad) {
@@ -287,8 +307,9 @@ int ctct_b200_loss_backward(const float *grads3, const float *grad_out, const in
     if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
     if (N == 0 || T == 0) return CTCT_OK;
     if (!grads3 || !grad_out || !lx || !ly || !dense || (U1 > 1 && !ys)) return CTCT_ERR_ARG;
-    ScatterArgs a;
-    a.GR = grads3;
+    if (reinterpret_cast<uintptr_t>(grads3) % 16) return CTCT_ERR_ARG;
+    DenseArgs a;
+    a.GR = reinterpret_cast<const float4 *>(grads3);
     a.grad_out = grad_out;
     a.ys = ys;
     a.lx = lx;
@@ -296,18 +317,17 @@ int ctct_b200_loss_backward(const float *grads3, const float *grad_out, const in
     a.out = dense;
     a.T = (int)T;
     a.U1 = (int)U1;
-    a.U1p = (int)pad4(U1);
     a.V = (int)V;
-    a.rows = N * T * U1;
+    a.vec = 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
     cudaEvent_t *slot = prof_slot(1);
     prof_mark(slot, 0, st);
     int rc = CTCT_ERR_ARG;
     switch (dtype) {
-    case CTCT_F32: rc = launch_scatter_t<float>(a, st); break;
-    case CTCT_F16: rc = launch_scatter_t<__half>(a, st); break;
-    case CTCT_BF16: rc = launch_scatter_t<__nv_bfloat16>(a, st); break;
+    case CTCT_F32: rc = launch_dense_t<float>(a, N, st); break;
+    case CTCT_F16: rc = launch_dense_t<__half>(a, N, st); break;
+    case CTCT_BF16: rc = launch_dense_t<__nv_bfloat16>(a, N, st); break;
     }
     prof_mark(slot, 1, st);
     return rc;
@@ -333,12 +353,12 @@ int ctct_b200_gathered_forward(const float *gathered, const int32_t *ys, const i
     if (!workspace || workspace_bytes < w.total || reinterpret_cast<uintptr_t>(workspace) % 256) return CTCT_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     char *ws = static_cast<char *>(workspace);
-    const int64_t total = N * T * 3 * w.U1p;
+    const int64_t total = N * T * U1 * 4;
     if (total > 0) {
         const int64_t want = (total + 255) / 256;
         const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
         k_repack_gathered<<<static_cast<int>(want < cap ? want : cap), 256, 0, st>>>(
-            gathered, lx, ly, reinterpret_cast<float *>(ws + w.G), (int)T, (int)U1, w.U1p, total);
+            gathered, lx, ly, reinterpret_cast<float *>(ws + w.G), (int)T, (int)U1, total);
         int rc = check_launch("repack");
         if (rc) return rc;
     }
@@ -359,8 +379,7 @@ int ctct_b200_export_tables(const void *workspace, size_t workspace_bytes, const
     if (!workspace || workspace_bytes < w.total) return CTCT_ERR_WORKSPACE;
     const char *ws = static_cast<const char *>(workspace);
     ExportArgs e;
-    e.TAB = reinterpret_cast<const float *>(ws + w.TAB);
-    e.OFF = reinterpret_cast<const int *>(ws + w.OFF);
+    e.TAB = reinterpret_cast<const float4 *>(ws + w.TAB);
     e.llf = reinterpret_cast<const float *>(ws + w.LLF);
     e.lli = reinterpret_cast<const int *>(ws + w.LLI);
     e.lx = lx;
@@ -371,9 +390,6 @@ int ctct_b200_export_tables(const void *workspace, size_t workspace_bytes, const
     e.ll_beta = ll_beta;
     e.T = (int)T;
     e.U1 = (int)U1;
-    e.U1p = w.U1p;
-    e.NL = w.cfg.NL;
-    e.C = w.cfg.C;
     const int S = 2 * ((int)U1 - 1) + 1;
     const int64_t cells = T * S > 0 ? T * S : 1;
     dim3 grid((unsigned)((cells + 255) / 256), (unsigned)N);
@@ -381,7 +397,131 @@ int ctct_b200_export_tables(const void *workspace, size_t workspace_bytes, const
     return check_launch("export_tables");
 }
 
-int ctct_b200_profile_disable(void) {
+
+int ctct_b200_log_matmul(const float *lhs, int64_t lsb, int64_t lsi, int64_t lsk, const float *rhs, int64_t rsb,
+                         int64_t rsk, int64_t rsj, int64_t B, int64_t M, int64_t K, int64_t N, float *out,
+                         void *stream) {
+    if (B < 0 || M < 0 || K < 0 || N < 0 || B > 65535 || M > (int64_t(1) << 20) || N > (int64_t(1) << 20) ||
+        K > 0x7fffffff)
+        return CTCT_ERR_ARG;
+    if (B == 0 || M == 0 || N == 0) return CTCT_OK;
+    if (!out || (K > 0 && (!lhs || !rhs))) return CTCT_ERR_ARG;
+    return launch_logmm(lhs, lsb, lsi, lsk, rhs, rsb, rsk, rsj, B, M, K, N, out, static_cast<cudaStream_t>(stream));
+}
+
+int ctct_b200_log_matmul_backward(const float *grad_out, const float *lhs, const float *rhsT, const float *res,
+                                  int64_t B, int64_t M, int64_t K, int64_t N, float *grad_lhs, float *grad_rhsT,
+                                  void *stream) {
+    if (B < 0 || M < 0 || K < 0 || N < 0 || B > 65535 || K > 0x7fffffff || M > 0x7fffffff || N > 0x7fffffff)
+        return CTCT_ERR_ARG;
+    if (B == 0 || K == 0) return CTCT_OK;
+    if (!grad_out || !lhs || !rhsT || !res) return CTCT_ERR_ARG;
+    LogmmBwdArgs a = {};
+    a.lhs = lhs;
+    a.rhsT = rhsT;
+    a.res = res;
+    a.gout = grad_out;
+    a.grad_lhs = grad_lhs;
+    a.grad_rhsT = grad_rhsT;
+    a.M = (int)M;
+    a.Nc = (int)N;
+    a.K = (int)K;
+    return launch_logmm_bwd(a, B, static_cast<cudaStream_t>(stream));
+}
+
+int ctct_b200_simple_forward(const float *f, const float *g, const float *den, const int32_t *ys, const int32_t *lx,
+                             const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int want_grad,
+                             float *costs, float *grads3, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
+    if (N == 0) return CTCT_OK;
+    if (!f || !g || !lx || !ly || !costs || (U1 > 1 && !ys) || (want_grad && !grads3)) return CTCT_ERR_ARG;
+    WsLayout w;
+    if (!ws_layout(N, T, U1, want_grad, &w)) return CTCT_ERR_UNSUPPORTED;
+    if (!workspace || workspace_bytes < w.total || reinterpret_cast<uintptr_t>(workspace) % 256) return CTCT_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char *ws = static_cast<char *>(workspace);
+    ComposeArgs c;
+    c.f = f;
+    c.g = g;
+    c.den = den;
+    c.ys = ys;
+    c.lx = lx;
+    c.ly = ly;
+    c.G = reinterpret_cast<float *>(ws + w.G);
+    c.T = (int)T;
+    c.U1 = (int)U1;
+    c.V = (int)V;
+    c.total = N * T * U1 * 4;
+    if (c.total > 0) {
+        const int64_t want = (c.total + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+        k_simple_compose<<<static_cast<int>(want < cap ? want : cap), 256, 0, st>>>(c);
+        int rc = check_launch("simple_compose");
+        if (rc) return rc;
+    }
+    int rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st);
+    if (rc) return rc;
+    if (want_grad) rc = launch_fill_grad(w, ws, ys, lx, ly, grads3, 0, N, T, U1, st);
+    return rc;
+}
+
+int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const float *f, const float *g,
+                              const float *den, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
+                              int64_t T, int64_t U1, int64_t V, float *grad_f, float *grad_g, void *stream) {
+    if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
+    if (N == 0) return CTCT_OK;
+    if (!grads3 || !grad_out || !lx || !ly || (U1 > 1 && !ys) || (den && (!f || !g))) return CTCT_ERR_ARG;
+    if (!grad_f && !grad_g) return CTCT_OK;
+    if (reinterpret_cast<uintptr_t>(grads3) % 16) return CTCT_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const float4 *g4 = reinterpret_cast<const float4 *>(grads3);
+    if (den) {
+        LogmmBwdArgs a = {};
+        a.lhs = f;
+        a.rhsT = g;
+        a.res = den;
+        a.grads3 = g4;
+        a.scale = grad_out;
+        a.lx = lx;
+        a.ly = ly;
+        a.grad_lhs = grad_f;
+        a.grad_rhsT = grad_g;
+        a.M = (int)T;
+        a.Nc = (int)U1;
+        a.K = (int)V;
+        int rc = launch_logmm_bwd(a, N, st);
+        if (rc) return rc;
+    } else {
+        if (grad_f && cudaMemsetAsync(grad_f, 0, sizeof(float) * N * T * V, st) != cudaSuccess) return check_launch("memset grad_f");
+        if (grad_g && cudaMemsetAsync(grad_g, 0, sizeof(float) * N * U1 * V, st) != cudaSuccess) return check_launch("memset grad_g");
+    }
+    PatchArgs p;
+    p.grads3 = g4;
+    p.scale = grad_out;
+    p.ys = ys;
+    p.lx = lx;
+    p.ly = ly;
+    p.grad_f = grad_f;
+    p.grad_g = grad_g;
+    p.T = (int)T;
+    p.U1 = (int)U1;
+    p.V = (int)V;
+    if (grad_f && T > 0) {
+        dim3 grid((unsigned)((T * U1 + 255) / 256), (unsigned)N);
+        k_simple_patch_f<<<grid, 256, 0, st>>>(p);
+        int rc = check_launch("simple_patch_f");
+        if (rc) return rc;
+    }
+    if (grad_g) {
+        const int64_t warps = N * U1;
+        k_simple_patch_g<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(p, (int)N);
+        int rc = check_launch("simple_patch_g");
+        if (rc) return rc;
+    }
+    return CTCT_OK;
+}
+
+static int profile_disable_locked() {
     if (g_prof.ev) {
         for (int i = 0; i < 4 * g_prof.cap; ++i) cudaEventDestroy(g_prof.ev[i]);
         delete[] g_prof.ev;
@@ -391,9 +531,15 @@ int ctct_b200_profile_disable(void) {
     return CTCT_OK;
 }
 
+int ctct_b200_profile_disable(void) {
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    return profile_disable_locked();
+}
+
 int ctct_b200_profile_enable(int max_calls) {
     if (max_calls < 1 || max_calls > (1 << 20)) return CTCT_ERR_ARG;
-    ctct_b200_profile_disable();
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    profile_disable_locked();
     g_prof.ev = new cudaEvent_t[4 * static_cast<size_t>(max_calls)];
     g_prof.kind = new int[max_calls];
     g_prof.cap = max_calls;
@@ -411,6 +557,7 @@ int ctct_b200_profile_enable(int max_calls) {
 
 int ctct_b200_profile_read(float *ms, int *kind, int capacity) {
     if (!ms || !kind || capacity < 0) return CTCT_ERR_ARG;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
     const int n = g_prof.used < capacity ? g_prof.used : capacity;
     for (int i = 0; i < n; ++i) {
         cudaEvent_t *e = g_prof.ev + 4 * i;

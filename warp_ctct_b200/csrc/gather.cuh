@@ -12,13 +12,14 @@
 
 namespace ctct {
 
-// INTERNAL = true : out[n][t][slot][U1p]  (contexts fastest, padded to a multiple of 4;
-//                   padding and everything outside t < lx, u <= ly is written as 0)
+// INTERNAL = true : out[n][t][u] = one 16-byte record {blank, repeat-label, next-label, 0}, values
+//                   converted to log2 units and clamped at NEG; everything outside t < lx,
+//                   u <= ly is written as 0
 // INTERNAL = false: out[n][t][u][slot]    (the reference's (N,T,U+1,3) layout)
 template <typename InT, typename IdxT, bool INTERNAL>
 __global__ void __launch_bounds__(256)
 k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__restrict__ lx,
-          const int *__restrict__ ly, float *__restrict__ out, int T, int U1, int U1p, int V,
+          const int *__restrict__ ly, float *__restrict__ out, int T, int U1, int V,
           IdxT total, int valid_only) {
     constexpr int PER = 4;
     const IdxT stride = static_cast<IdxT>(gridDim.x) * blockDim.x;
@@ -35,10 +36,10 @@ k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__r
                 int u, k;
                 IdxT nt;
                 if (INTERNAL) {
-                    u = static_cast<int>(e % static_cast<IdxT>(U1p));
-                    const IdxT r = e / static_cast<IdxT>(U1p);
-                    k = static_cast<int>(r % 3);
-                    nt = r / 3;
+                    k = static_cast<int>(e & 3);
+                    const IdxT r = e >> 2;
+                    u = static_cast<int>(r % static_cast<IdxT>(U1));
+                    nt = r / static_cast<IdxT>(U1);
                 } else {
                     k = static_cast<int>(e % 3);
                     const IdxT r = e / 3;
@@ -47,7 +48,7 @@ k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__r
                 }
                 const int n = static_cast<int>(nt / static_cast<IdxT>(T));
                 const int t = static_cast<int>(nt - static_cast<IdxT>(n) * T);
-                bool take = u < U1;
+                bool take = k < 3;
                 if (valid_only) take = take && t < lx[n] && u <= ly[n];
                 if (take) {
                     int idx = 0;
@@ -56,7 +57,8 @@ k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__r
                     if (k == 2 && u < U && (!valid_only || u < ly[n])) idx = ys[static_cast<int64_t>(n) * U + u];
                     idx = min(max(idx, 0), V - 1);
                     const int64_t row = static_cast<int64_t>(nt) * U1 + u;
-                    val[j] = load_as_float(lp + row * V + idx);
+                    const float x = load_as_float(lp + row * V + idx);
+                    val[j] = INTERNAL ? to_log2(x) : x;
                 }
             }
         }
@@ -68,21 +70,21 @@ k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__r
     }
 }
 
-// (N,T,U1,3) reference layout -> internal layout, zeroing everything outside the valid region.
+// (N,T,U1,3) reference layout -> internal layout (log2 units), zeroing everything outside the valid region.
 // Used when the caller hands in pre-gathered log-probs (csrc/binding.cpp:31-34 interface).
 __global__ void __launch_bounds__(256)
 k_repack_gathered(const float *__restrict__ g, const int *__restrict__ lx, const int *__restrict__ ly,
-                  float *__restrict__ out, int T, int U1, int U1p, int64_t total) {
+                  float *__restrict__ out, int T, int U1, int64_t total) {
     for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
          e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int u = static_cast<int>(e % U1p);
-        const int64_t r = e / U1p;
-        const int k = static_cast<int>(r % 3);
-        const int64_t nt = r / 3;
+        const int k = static_cast<int>(e & 3);
+        const int64_t r = e >> 2;
+        const int u = static_cast<int>(r % U1);
+        const int64_t nt = r / U1;
         const int n = static_cast<int>(nt / T);
         const int t = static_cast<int>(nt - static_cast<int64_t>(n) * T);
         float v = 0.0f;
-        if (u < U1 && t < lx[n] && u <= ly[n]) v = g[(nt * U1 + u) * 3 + k];
+        if (k < 3 && t < lx[n] && u <= ly[n]) v = to_log2(g[(nt * U1 + u) * 3 + k]);
         out[e] = v;
     }
 }

@@ -1,12 +1,14 @@
 // Gradient kernels.
 //
-//  k_fill_grad   : occupancy gradient w.r.t. the three gathered log-probs of every (n,t,u),
-//                  the quantity the reference's k_fill_grad produces (csrc/gather.cu:311-374),
-//                  evaluated from the normalised tables of lattice.cuh.
-//  k_scatter_*   : the dense (N,T,U+1,V) gradient in ONE pass of 16-byte stores: zeros
-//                  everywhere except <= 3 patched columns per row.  Replaces what autograd does
-//                  for the reference after CTCTLoss.backward (warp_ctct/__init__.py:31-33): a
-//                  multiply, a cast, a memset of the full tensor and a scatter_add.
+//  k_fill_grad    : occupancy gradient w.r.t. the three gathered log-probs of every (n,t,u),
+//                   the quantity the reference's k_fill_grad produces (csrc/gather.cu:311-374),
+//                   evaluated from the normalised tables of lattice.cuh.
+//  k_dense_grad   : the dense (N,T,U+1,V) gradient in ONE pass, every byte written once with
+//                   16-byte stores: zeros everywhere except <= 3 columns per row, which are
+//                   patched in registers before the store.
+//                   Replaces what autograd does for the reference after CTCTLoss.backward
+//                   (warp_ctct/__init__.py:31-33): a multiply, a cast, a memset of the full tensor
+//                   and a scatter_add.
 //  k_export_tables: test hook, tables in natural-log units and unshifted coordinates.
 #pragma once
 
@@ -14,15 +16,41 @@
 
 namespace ctct {
 
+// occupancies of the arcs leaving context u at frame t: {blank, repeat label, next label}
+__device__ __forceinline__ float3 occupancies(const float4 *__restrict__ G, const float4 *__restrict__ TAB,
+                                              const int *__restrict__ y, int64_t nt, int u, int U1, int Un, float lf,
+                                              int li) {
+    const float4 p = G[nt * U1 + u];
+    const float4 av = TAB[(nt * 2 + 0) * U1 + u];
+    const float4 bv = TAB[(nt * 2 + 1) * U1 + u];
+    const float aL = av.x, aB = av.y, bL = bv.x, bB = bv.y;
+    const int oA = __float_as_int(av.z);
+    const float c_same = static_cast<float>(oA + __float_as_int(bv.z) - li) - lf;
+    // arcs leaving the blank state 2u: stay (blank), or emit label u
+    float occ0 = ex2(aB + bB + p.x + c_same);
+    float occ1 = 0.0f, occ2 = 0.0f;
+    if (u >= 1) {
+        // arcs leaving the label state 2u-1: to blank 2u, stay (repeat label u-1)
+        occ0 += ex2(aL + bB + p.x + c_same);
+        occ1 = ex2(aL + bL + p.y + c_same);
+    }
+    if (u < Un) {
+        const float4 bn = TAB[(nt * 2 + 1) * U1 + u + 1];
+        const float c_next = static_cast<float>(oA + __float_as_int(bn.z) - li) - lf;
+        occ2 = ex2(aB + bn.x + p.z + c_next);
+        if (u >= 1 && y[u] != y[u - 1]) occ2 += ex2(aL + bn.x + p.z + c_next);
+    }
+    return make_float3(occ0, occ1, occ2);
+}
+
 struct GradArgs {
-    const float *G;    // [N][T][3][U1p]
-    const float *TAB;  // [N][T][4][U1p]
-    const int *OFF;    // [N][T][2][NL]
-    const float *llf;  // [N][2]
-    const int *lli;    // [N][2]
+    const float4 *G;    // [N][T][U1], log2 units
+    const float4 *TAB;  // [N][T][2][U1]
+    const float *llf;   // [N][2]
+    const int *lli;     // [N][2]
     const int *ys, *lx, *ly;
-    float *out;        // internal [N][T][3][U1p] or reference [N][T][U1][3]
-    int T, U1, U1p, NL, C;
+    float *out;         // internal [N][T][U1] float4 {g0,g1,g2,0} or reference [N][T][U1][3]
+    int T, U1;
     int ref_layout;
 };
 
@@ -37,56 +65,24 @@ __global__ void __launch_bounds__(256) k_fill_grad(const GradArgs a) {
     if (idx >= cells) return;
     const int t = idx / a.U1;
     const int u = idx - t * a.U1;
-    const int U1p = a.U1p, U = a.U1 - 1;
+    const int U = a.U1 - 1;
     const int Tn = max(0, min(a.lx[n], a.T));
     const int Un = max(0, min(a.ly[n], U));
     const int64_t nt = static_cast<int64_t>(n) * a.T + t;
 
-    float g0 = 0.0f, g1 = 0.0f, g2 = 0.0f;
+    float3 g = make_float3(0.0f, 0.0f, 0.0f);
     const float lf = a.llf[n * 2 + 1];
     if (t < Tn && u <= Un && lf > NEG_TEST) {
-        const int li = a.lli[n * 2 + 1];
-        const float *row = a.G + nt * 3 * U1p;
-        const float *tab = a.TAB + nt * 4 * U1p;
-        const int *off = a.OFF + nt * 2 * a.NL;
-        const float aL = tab[u], aB = tab[U1p + u];
-        const float bL = tab[2 * U1p + u], bB = tab[3 * U1p + u];
-        const float p0 = to_log2(row[u]), p1 = to_log2(row[U1p + u]), p2 = to_log2(row[2 * U1p + u]);
-        const int la = u / a.C;
-        const int oA = off[la];
-        const float c_same = static_cast<float>(oA + off[a.NL + la] - li) - lf;
-        // arcs leaving the blank state 2u: stay (blank), or emit label u
-        float occ0 = ex2(aB + bB + p0 + c_same);
-        float occ1 = 0.0f, occ2 = 0.0f;
-        if (u >= 1) {
-            // arcs leaving the label state 2u-1: to blank 2u, stay (repeat label u-1)
-            occ0 += ex2(aL + bB + p0 + c_same);
-            occ1 = ex2(aL + bL + p1 + c_same);
-        }
-        if (u < Un) {
-            const int lb = (u + 1) / a.C;
-            const float bLn = tab[2 * U1p + u + 1];
-            const float c_next = static_cast<float>(oA + off[a.NL + lb] - li) - lf;
-            occ2 = ex2(aB + bLn + p2 + c_next);
-            if (u >= 1) {
-                const int *y = a.ys + static_cast<int64_t>(n) * U;
-                if (y[u] != y[u - 1]) occ2 += ex2(aL + bLn + p2 + c_next);
-            }
-        }
-        g0 = -occ0;
-        g1 = -occ1;
-        g2 = -occ2;
+        const float3 occ = occupancies(a.G, a.TAB, a.ys + static_cast<int64_t>(n) * U, nt, u, a.U1, Un, lf, a.lli[n * 2 + 1]);
+        g = make_float3(-occ.x, -occ.y, -occ.z);
     }
     if (a.ref_layout) {
         float *o = a.out + (nt * a.U1 + u) * 3;
-        o[0] = g0;
-        o[1] = g1;
-        o[2] = g2;
+        o[0] = g.x;
+        o[1] = g.y;
+        o[2] = g.z;
     } else {
-        float *o = a.out + nt * 3 * U1p + u;
-        o[0] = g0;
-        o[U1p] = g1;
-        o[2 * U1p] = g2;
+        reinterpret_cast<float4 *>(a.out)[nt * a.U1 + u] = make_float4(g.x, g.y, g.z, 0.0f);
     }
 }
 
@@ -100,103 +96,151 @@ struct OutOps<float> {
     static constexpr int E = 4;  // elements per 16-byte store
     __device__ static float cvt(float x) { return x; }
     __device__ static float add(float a, float b) { return a + b; }
-    __device__ static unsigned bits(float x) { return __float_as_uint(x); }
 };
 template <>
 struct OutOps<__half> {
     static constexpr int E = 8;
     __device__ static __half cvt(float x) { return __float2half_rn(x); }
     __device__ static __half add(__half a, __half b) { return __hadd(a, b); }
-    __device__ static unsigned bits(__half x) { return __half_as_ushort(x); }
 };
 template <>
 struct OutOps<__nv_bfloat16> {
     static constexpr int E = 8;
     __device__ static __nv_bfloat16 cvt(float x) { return __float2bfloat16_rn(x); }
     __device__ static __nv_bfloat16 add(__nv_bfloat16 a, __nv_bfloat16 b) { return __hadd(a, b); }
-    __device__ static unsigned bits(__nv_bfloat16 x) { return __bfloat16_as_ushort(x); }
 };
 
-struct ScatterArgs {
-    const float *GR;        // [N][T][3][U1p] compact gradient
+struct DenseArgs {
+    const float4 *GR;       // [N][T][U1] compact gradient {g0,g1,g2,0}
     const float *grad_out;  // [N]
     const int *ys, *lx, *ly;
     void *out;              // [N][T][U1][V]
-    int T, U1, U1p, V;
-    int64_t rows;           // N*T*U1
+    int T, U1, V;
+    int vec;                // 1: V is a multiple of the 16-byte vector width and the base is 16-byte aligned
 };
 
-// value of column `col` of a row whose three patched columns are 0, i1, i2
+// What one row of the dense gradient holds besides zeros: column 0 and up to two label columns.
 template <typename OutT>
-__device__ __forceinline__ OutT patched(int col, int i1, int i2, OutT v0, OutT v1, OutT v2, bool has1, bool has2) {
-    OutT acc = OutOps<OutT>::cvt(0.0f);
-    if (col == 0) acc = OutOps<OutT>::add(acc, v0);
-    if (has1 && col == i1) acc = OutOps<OutT>::add(acc, v1);
-    if (has2 && col == i2) acc = OutOps<OutT>::add(acc, v2);
-    return acc;
+struct RowPatch {
+    OutT c0, c1, c2;
+    int i1, i2;  // label columns, -1 when absent (or merged into an earlier column)
+};
+
+// Columns that coincide add up in slot order, each product rounded to OutT first -- what a
+// cast followed by scatter_add onto zeros produces.
+template <typename OutT>
+__device__ __forceinline__ RowPatch<OutT> make_patch(const float4 g, float go, const int *__restrict__ y, int u, int Un,
+                                                     int V) {
+    using O = OutOps<OutT>;
+    RowPatch<OutT> p;
+    const OutT zero = O::cvt(0.0f);
+    p.c0 = O::add(zero, O::cvt(go * g.x));
+    p.c1 = zero;
+    p.c2 = zero;
+    p.i1 = -1;
+    p.i2 = -1;
+    if (u >= 1) {
+        p.i1 = min(max(y[u - 1], 0), V - 1);
+        p.c1 = O::add(zero, O::cvt(go * g.y));
+    }
+    if (u < Un) {
+        p.i2 = min(max(y[u], 0), V - 1);
+        p.c2 = O::add(zero, O::cvt(go * g.z));
+    }
+    if (p.i1 == 0) {
+        p.c0 = O::add(p.c0, p.c1);
+        p.i1 = -1;
+    }
+    if (p.i2 == 0) {
+        p.c0 = O::add(p.c0, p.c2);
+        p.i2 = -1;
+    }
+    if (p.i1 >= 0 && p.i1 == p.i2) {
+        p.c1 = O::add(p.c1, p.c2);
+        p.i2 = -1;
+    }
+    return p;
 }
 
-// One warp per vocabulary row, rows dealt round-robin to warps so that at any moment the
-// grid writes one contiguous window of the tensor.  VEC = true: V is a multiple of the
-// vector width and the base is 16-byte aligned, every lane issues st.global.v4.
-template <typename OutT, bool VEC>
-__global__ void __launch_bounds__(256) k_scatter_dense(const ScatterArgs a) {
-    constexpr int E = OutOps<OutT>::E;
-    const int lane = threadIdx.x & 31;
-    const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-    const int U = a.U1 - 1, V = a.V;
-    OutT *out = static_cast<OutT *>(a.out);
+template <typename OutT>
+__device__ __forceinline__ unsigned out_bits(OutT x);
+template <>
+__device__ __forceinline__ unsigned out_bits<float>(float x) { return __float_as_uint(x); }
+template <>
+__device__ __forceinline__ unsigned out_bits<__half>(__half x) { return __half_as_ushort(x); }
+template <>
+__device__ __forceinline__ unsigned out_bits<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat16_as_ushort(x); }
 
-    for (int64_t r = warp0; r < a.rows; r += nwarps) {
-        const int64_t nt = r / a.U1;
-        const int u = static_cast<int>(r - nt * a.U1);
-        const int n = static_cast<int>(nt / a.T);
-        const int t = static_cast<int>(nt - static_cast<int64_t>(n) * a.T);
-        const int Tn = min(a.lx[n], a.T), Un = min(a.ly[n], U);
-        OutT v0 = OutOps<OutT>::cvt(0.0f), v1 = v0, v2 = v0;
-        int i1 = -1, i2 = -1;
-        bool has1 = false, has2 = false;
-        const bool valid = t < Tn && u <= Un;
-        if (valid) {
-            const float go = a.grad_out[n];
-            const float *g = a.GR + nt * 3 * a.U1p + u;
-            v0 = OutOps<OutT>::cvt(go * g[0]);
-            if (u >= 1) {
-                has1 = true;
-                i1 = min(max(a.ys[static_cast<int64_t>(n) * U + u - 1], 0), V - 1);
-                v1 = OutOps<OutT>::cvt(go * g[a.U1p]);
+// One CTA per (n,t) slab of U1 rows; inside, one warp per row (rows dealt round-robin to the 8
+// warps), lanes stride over the row in 16-byte vectors.  A lane patches the non-zero columns
+// in its own registers before the store, so every byte is written exactly once and nothing
+// waits on anything: the only loads are one 16-byte record and two labels per row, issued one
+// row ahead.  Many short CTAs (not a persistent grid) is what reaches the HBM write peak here.
+template <typename OutT>
+__global__ void __launch_bounds__(256) k_dense_grad(const DenseArgs a) {
+    constexpr int E = OutOps<OutT>::E;
+    const int64_t slab = blockIdx.x;  // = n*T + t
+    const int n = static_cast<int>(slab / a.T);
+    const int t = static_cast<int>(slab - static_cast<int64_t>(n) * a.T);
+    const int U = a.U1 - 1, V = a.V;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    OutT *base = static_cast<OutT *>(a.out) + slab * static_cast<int64_t>(a.U1) * V;
+    const int Tn = min(a.lx[n], a.T);
+    const int Un = (t < Tn) ? min(a.ly[n], U) : -1;  // rows u <= Un carry values
+    const int *y = a.ys + static_cast<int64_t>(n) * U;
+    const float go = (Un >= 0) ? a.grad_out[n] : 0.0f;
+    const float4 *gr = a.GR + slab * a.U1;
+
+    float4 g_next = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (warp <= Un) g_next = gr[warp];
+    for (int u = warp; u < a.U1; u += 8) {
+        const float4 g = g_next;
+        if (u + 8 <= Un) g_next = gr[u + 8];
+        OutT *row = base + static_cast<int64_t>(u) * V;
+        if (u > Un) {  // padding row
+            if (a.vec) {
+                uint4 *dv = reinterpret_cast<uint4 *>(row);
+                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                for (int j = lane; j < V / E; j += 32) dv[j] = z;
+            } else {
+                const OutT z = OutOps<OutT>::cvt(0.0f);
+                for (int c = lane; c < V; c += 32) row[c] = z;
             }
-            if (u < Un) {
-                has2 = true;
-                i2 = min(max(a.ys[static_cast<int64_t>(n) * U + u], 0), V - 1);
-                v2 = OutOps<OutT>::cvt(go * g[2 * a.U1p]);
-            }
+            continue;
         }
-        OutT *dst = out + r * V;
-        if (VEC) {
-            const int nvec = V / E;
-            const int j1 = has1 ? i1 / E : -1, j2 = has2 ? i2 / E : -1;
-            uint4 *dv = reinterpret_cast<uint4 *>(dst);
-            for (int j = lane; j < nvec; j += 32) {
+        const RowPatch<OutT> p = make_patch<OutT>(g, go, y, u, Un, V);
+        if (a.vec) {
+            uint4 *dv = reinterpret_cast<uint4 *>(row);
+            const int j1 = p.i1 >= 0 ? p.i1 / E : -1, j2 = p.i2 >= 0 ? p.i2 / E : -1;
+            for (int j = lane; j < V / E; j += 32) {
                 uint4 w = make_uint4(0u, 0u, 0u, 0u);
-                if (valid && (j == 0 || j == j1 || j == j2)) {
+                if (j == 0 || j == j1 || j == j2) {
                     unsigned b[E];
 #pragma unroll
-                    for (int e = 0; e < E; ++e)
-                        b[e] = OutOps<OutT>::bits(patched<OutT>(j * E + e, i1, i2, v0, v1, v2, has1, has2));
+                    for (int e = 0; e < E; ++e) {
+                        const int col = j * E + e;
+                        OutT x = OutOps<OutT>::cvt(0.0f);
+                        if (col == 0) x = p.c0;
+                        if (col == p.i1) x = p.c1;
+                        if (col == p.i2) x = p.c2;
+                        b[e] = out_bits<OutT>(x);
+                    }
                     if constexpr (E == 4) {
                         w = make_uint4(b[0], b[1], b[2], b[3]);
                     } else {
-                        w = make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16),
-                                       b[6] | (b[7] << 16));
+                        w = make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16));
                     }
                 }
-                __stcs(dv + j, w);
+                dv[j] = w;
             }
         } else {
-            for (int col = lane; col < V; col += 32)
-                dst[col] = valid ? patched<OutT>(col, i1, i2, v0, v1, v2, has1, has2) : OutOps<OutT>::cvt(0.0f);
+            for (int c = lane; c < V; c += 32) {
+                OutT x = OutOps<OutT>::cvt(0.0f);
+                if (c == 0) x = p.c0;
+                if (c == p.i1) x = p.c1;
+                if (c == p.i2) x = p.c2;
+                row[c] = x;
+            }
         }
     }
 }
@@ -205,13 +249,12 @@ __global__ void __launch_bounds__(256) k_scatter_dense(const ScatterArgs a) {
 // test hook
 
 struct ExportArgs {
-    const float *TAB;
-    const int *OFF;
+    const float4 *TAB;
     const float *llf;
     const int *lli;
     const int *lx, *ly;
     double *alpha, *beta_next, *ll_alpha, *ll_beta;
-    int T, U1, U1p, NL, C;
+    int T, U1;
 };
 
 __global__ void __launch_bounds__(256) k_export_tables(const ExportArgs a) {
@@ -229,17 +272,16 @@ __global__ void __launch_bounds__(256) k_export_tables(const ExportArgs a) {
     }
     if (idx >= cells) return;
     const int t = idx / S, s = idx - t * S;
-    const int u = (s + 1) / 2, kind = (s & 1) ? 0 : 1;  // label state 2u-1 -> slot 0, blank 2u -> slot 1
+    const int u = (s + 1) / 2;
+    const bool blank = (s & 1) == 0;
     const int Tn = max(0, min(a.lx[n], a.T)), Un = max(0, min(a.ly[n], U));
     const int64_t nt = static_cast<int64_t>(n) * a.T + t;
     double va = ninf, vb = ninf;
     if (t < Tn && u <= Un) {
-        const float *tab = a.TAB + nt * 4 * a.U1p;
-        const int *off = a.OFF + nt * 2 * a.NL;
-        const int l = u / a.C;
-        const float x = tab[kind * a.U1p + u], y = tab[(2 + kind) * a.U1p + u];
-        if (x > NEG_TEST) va = (static_cast<double>(off[l]) + x) * LN2;
-        if (y > NEG_TEST) vb = (static_cast<double>(off[a.NL + l]) + y) * LN2;
+        const float4 av = a.TAB[(nt * 2 + 0) * a.U1 + u], bv = a.TAB[(nt * 2 + 1) * a.U1 + u];
+        const float x = blank ? av.y : av.x, y = blank ? bv.y : bv.x;
+        if (x > NEG_TEST) va = (static_cast<double>(__float_as_int(av.z)) + x) * LN2;
+        if (y > NEG_TEST) vb = (static_cast<double>(__float_as_int(bv.z)) + y) * LN2;
     }
     a.alpha[nt * S + s] = va;
     a.beta_next[nt * S + s] = vb;

@@ -1,0 +1,260 @@
+// Kernels of the log-add joiner ("simple") loss: log-probs are composed on the fly as
+// f[n,t,v] + g[n,u,v] - den[n,t,u] with den = log sum_v exp(f + g)  (csrc/simple.cu:20-26,
+// csrc/simple_unnorm.cu:20-25 without den, warp_ctct/__init__.py:195-215).
+//
+//  k_logmm_exact      : batched log-semiring product with a per-output running maximum, any
+//                       strides, any dynamic range (the contract of csrc/logmatmul.cu:44-146).
+//  k_simple_compose   : gathers of f and g fused with the f+g-den composition, straight into the
+//                       lattice's internal 3-slot layout (replaces the two torch.gather calls of
+//                       warp_ctct/__init__.py:204-215 and the LOGPROB macros of simple.cu).
+//  k_logmm_bwd_exact  : backward of the log-semiring product in linear space,
+//                       grad_lhs = sum_j grad_out * exp(lhs + rhs - res) (csrc/binding.cpp:251-253);
+//                       the exponent is <= 0, so no sign split or log-space detour is needed.
+//  k_simple_patch_*   : adds the lattice's own sparse gradient (blank / label columns) on top,
+//                       the reductions of csrc/binding.cpp:198,209-219 plus the gather backwards.
+#pragma once
+
+#include "common.cuh"
+
+namespace ctct {
+
+constexpr float LN2F = 0.6931471805599453f;
+
+struct LogmmArgs {
+    const float *lhs, *rhs;
+    float *out;  // (B, M, N) contiguous
+    int64_t lsb, lsi, lsk, rsb, rsk, rsj;
+    int M, K, N;
+};
+
+// 32x32 output tile per 256-thread block, 4 outputs per thread, K in chunks of 32 through
+// shared memory.  Per chunk: chunk maximum first, one rescale of the running sum, then one
+// exp per term.  A row/column pair whose terms are all -inf yields -inf.
+__global__ void __launch_bounds__(256) k_logmm_exact(const LogmmArgs a) {
+    __shared__ float As[32][33];  // [i][k]
+    __shared__ float Bs[32][33];  // [k][j]
+    const int b = blockIdx.z;
+    const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // ty in [0,8)
+    const float NINF = -__int_as_float(0x7f800000);
+    const float *lhs = a.lhs + b * a.lsb;
+    const float *rhs = a.rhs + b * a.rsb;
+    const bool rhs_k_fast = (a.rsk == 1) || (a.rsj != 1);
+
+    float m[4], s[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        m[r] = NINF;
+        s[r] = 0.0f;
+    }
+    for (int k0 = 0; k0 < a.K; k0 += 32) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int ii = ty + 8 * r;
+            const int gi = i0 + ii, gk = k0 + tx;
+            As[ii][tx] = (gi < a.M && gk < a.K) ? __ldg(lhs + gi * a.lsi + gk * a.lsk) : NINF;
+            if (rhs_k_fast) {  // tx runs along k
+                const int gj = j0 + ii;
+                Bs[tx][ii] = (gj < a.N && gk < a.K) ? __ldg(rhs + gk * a.rsk + gj * a.rsj) : NINF;
+            } else {  // tx runs along j
+                const int kk = k0 + ii, gj = j0 + tx;
+                Bs[ii][tx] = (gj < a.N && kk < a.K) ? __ldg(rhs + kk * a.rsk + gj * a.rsj) : NINF;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int ii = ty + 8 * r;
+            float cm = NINF;
+#pragma unroll 8
+            for (int k = 0; k < 32; ++k) cm = fmaxf(cm, As[ii][k] + Bs[k][tx]);
+            const float mn = fmaxf(m[r], cm);
+            if (mn > NINF && mn < -NINF) {
+                float acc = s[r] * ex2((m[r] - mn) * LOG2E);  // m == -inf -> s == 0 stays 0
+                if (!(m[r] > NINF)) acc = 0.0f;
+#pragma unroll 8
+                for (int k = 0; k < 32; ++k) acc += ex2((As[ii][k] + Bs[k][tx] - mn) * LOG2E);
+                s[r] = acc;
+                m[r] = mn;
+            } else if (mn == -NINF) {  // +inf term: result is +inf
+                m[r] = mn;
+                s[r] = 1.0f;
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int gi = i0 + ty + 8 * r, gj = j0 + tx;
+        if (gi < a.M && gj < a.N)
+            a.out[(static_cast<int64_t>(b) * a.M + gi) * a.N + gj] = (m[r] > NINF) ? m[r] + lg2(s[r]) * LN2F : NINF;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+
+struct ComposeArgs {
+    const float *f;    // (N,T,V)
+    const float *g;    // (N,U1,V)
+    const float *den;  // (N,T,U1) or nullptr
+    const int *ys, *lx, *ly;
+    float *G;          // [N][T][U1][4] records {blank, repeat-label, next-label, 0}, log2 units
+    int T, U1, V;
+    int64_t total;     // N*T*U1*4
+};
+
+__global__ void __launch_bounds__(256) k_simple_compose(const ComposeArgs a) {
+    const int U = a.U1 - 1;
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < a.total;
+         e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int k = static_cast<int>(e & 3);
+        const int64_t r = e >> 2;
+        const int u = static_cast<int>(r % a.U1);
+        const int64_t nt = r / a.U1;
+        const int n = static_cast<int>(nt / a.T);
+        float v = 0.0f;
+        const int t = static_cast<int>(nt - static_cast<int64_t>(n) * a.T);
+        if (k < 3 && t < a.lx[n] && u <= a.ly[n]) {
+            int idx = 0;
+            if (k == 1 && u >= 1) idx = a.ys[static_cast<int64_t>(n) * U + u - 1];
+            if (k == 2 && u < a.ly[n]) idx = a.ys[static_cast<int64_t>(n) * U + u];
+            idx = min(max(idx, 0), a.V - 1);
+            float x = __ldg(a.f + nt * a.V + idx) + __ldg(a.g + (static_cast<int64_t>(n) * a.U1 + u) * a.V + idx);
+            if (a.den) x -= __ldg(a.den + nt * a.U1 + u);
+            v = to_log2(x);
+        }
+        a.G[e] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+
+struct LogmmBwdArgs {
+    const float *lhs;       // (B,M,K) contiguous       [f]
+    const float *rhsT;      // (B,Nc,K) contiguous      [g, i.e. rhs transposed]
+    const float *res;       // (B,M,Nc) contiguous      [den]
+    const float *gout;      // (B,M,Nc) contiguous, any sign; or nullptr with the fields below
+    const float4 *grads3;   // [B][M][Nc] records {g0,g1,g2,0}: grad_out = -scale[b] * sum of the three slots
+    const float *scale;     // [B]
+    const int *lx, *ly;     // valid extents (rows < lx[b], columns <= ly[b]); nullptr = all valid
+    float *grad_lhs;        // (B,M,K) or nullptr
+    float *grad_rhsT;       // (B,Nc,K) or nullptr
+    int M, Nc, K;
+};
+
+// One thread per k (vocabulary entry), VT threads per block; the block walks all (i,j) of one
+// batch entry.  grad_rhs is accumulated over i in shared memory ([Nc][VT]), grad_lhs over j
+// in a register.  The rhs tile ([Nc][VT]) is cached in shared memory as well.
+template <int VT>
+__global__ void __launch_bounds__(VT) k_logmm_bwd_exact(const LogmmBwdArgs a) {
+    extern __shared__ float sm[];
+    const int b = blockIdx.y;
+    const int k = blockIdx.x * VT + threadIdx.x;
+    const bool kin = k < a.K;
+    float *gT = sm;                                   // [Nc][VT]  rhs tile in log2 units
+    float *acc = sm + static_cast<size_t>(a.Nc) * VT;  // [Nc][VT]  grad_rhs accumulators
+    float *wrow = acc + static_cast<size_t>(a.Nc) * VT;  // [Nc] weight row, [Nc] res row
+    float *drow = wrow + a.Nc;
+    const int Mv = a.lx ? max(0, min(a.lx[b], a.M)) : a.M;
+    const int Nv = a.ly ? max(0, min(a.ly[b] + 1, a.Nc)) : a.Nc;
+    for (int j = 0; j < a.Nc; ++j) {
+        gT[j * VT + threadIdx.x] = kin ? __ldg(a.rhsT + (static_cast<int64_t>(b) * a.Nc + j) * a.K + k) * LOG2E : 0.0f;
+        acc[j * VT + threadIdx.x] = 0.0f;
+    }
+    for (int i = 0; i < a.M; ++i) {
+        const int64_t bi = static_cast<int64_t>(b) * a.M + i;
+        float accF = 0.0f;
+        if (i < Mv) {
+            __syncthreads();
+            for (int j = threadIdx.x; j < Nv; j += VT) {
+                float w;
+                if (a.gout) {
+                    w = a.gout[bi * a.Nc + j];
+                } else {
+                    const float4 g3 = a.grads3[bi * a.Nc + j];
+                    w = -a.scale[b] * (g3.x + g3.y + g3.z);
+                }
+                wrow[j] = w;
+                drow[j] = a.res[bi * a.Nc + j] * LOG2E;
+            }
+            __syncthreads();
+            const float fv = kin ? __ldg(a.lhs + bi * a.K + k) * LOG2E : 0.0f;
+            for (int j = 0; j < Nv; ++j) {
+                const float w = wrow[j];
+                if (w != 0.0f) {
+                    const float p = w * ex2(fv + gT[j * VT + threadIdx.x] - drow[j]);
+                    accF += p;
+                    acc[j * VT + threadIdx.x] += p;
+                }
+            }
+        }
+        if (a.grad_lhs && kin) a.grad_lhs[bi * a.K + k] = accF;
+    }
+    if (a.grad_rhsT && kin)
+        for (int j = 0; j < a.Nc; ++j)
+            a.grad_rhsT[(static_cast<int64_t>(b) * a.Nc + j) * a.K + k] = acc[j * VT + threadIdx.x];
+}
+
+// ---------------------------------------------------------------------------------------
+
+struct PatchArgs {
+    const float4 *grads3; // [N][T][U1] records {g0,g1,g2,0}
+    const float *scale;   // [N]
+    const int *ys, *lx, *ly;
+    float *grad_f;        // (N,T,V) or nullptr
+    float *grad_g;        // (N,U1,V) or nullptr
+    int T, U1, V;
+};
+
+// grad_f[n,t,0] += sum_u g0;  grad_f[n,t,ys[j]] += g2[t,j] + g1[t,j+1].  One thread per (t, j);
+// labels may repeat inside an utterance, hence atomics.
+__global__ void __launch_bounds__(256) k_simple_patch_f(const PatchArgs a) {
+    const int n = blockIdx.y;
+    const int U = a.U1 - 1;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= a.T * a.U1) return;
+    const int t = idx / a.U1, j = idx - t * a.U1;
+    const int Tn = max(0, min(a.lx[n], a.T)), Un = max(0, min(a.ly[n], U));
+    if (t >= Tn || j > Un) return;
+    const int64_t nt = static_cast<int64_t>(n) * a.T + t;
+    const float4 *g3 = a.grads3 + nt * a.U1;
+    const float sc = a.scale[n];
+    float *row = a.grad_f + nt * a.V;
+    atomicAdd(row, sc * g3[j].x);  // blank column collects slot 0 of every context
+    if (j < Un) {
+        const int v = min(max(a.ys[static_cast<int64_t>(n) * U + j], 0), a.V - 1);
+        atomicAdd(row + v, sc * (g3[j].z + g3[j + 1].y));
+    }
+}
+
+// grad_g[n,u,{0, ys[u-1], ys[u]}] += sum_t of the three slots.  One warp per (n,u).
+__global__ void __launch_bounds__(256) k_simple_patch_g(const PatchArgs a, int N) {
+    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (w >= N * a.U1) return;
+    const int n = w / a.U1, u = w - n * a.U1;
+    const int U = a.U1 - 1;
+    const int Tn = max(0, min(a.lx[n], a.T)), Un = max(0, min(a.ly[n], U));
+    if (u > Un) return;
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f;
+    for (int t = lane; t < Tn; t += 32) {
+        const float4 g3 = a.grads3[(static_cast<int64_t>(n) * a.T + t) * a.U1 + u];
+        s0 += g3.x;
+        s1 += g3.y;
+        s2 += g3.z;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if (lane == 0) {
+        const float sc = a.scale[n];
+        float *row = a.grad_g + (static_cast<int64_t>(n) * a.U1 + u) * a.V;
+        row[0] += sc * s0;
+        if (u >= 1) row[min(max(a.ys[static_cast<int64_t>(n) * U + u - 1], 0), a.V - 1)] += sc * s1;
+        if (u < Un) row[min(max(a.ys[static_cast<int64_t>(n) * U + u], 0), a.V - 1)] += sc * s2;
+    }
+}
+
+}  // namespace ctct

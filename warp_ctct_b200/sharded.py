@@ -1,0 +1,97 @@
+"""Batch-sharded CTC-T loss: one process per GPU, utterances split across ranks.
+
+Utterances are independent in every kernel, so the data path needs no collective at all; the
+only exchange is one all-reduce of the scalar sum of costs (4 bytes) so that every rank holds
+the global loss.  The reference has no multi-GPU code; the reduction semantics are those of
+warp_ctct/__init__.py:138-147 applied to the GLOBAL batch.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from . import FusedCTCTLoss, _as_int, _require_cuda
+
+
+def plan_shards(frames_lengths: Sequence[int], labels_lengths: Sequence[int], world_size: int) -> List[List[int]]:
+    """Length-balanced assignment of utterances to ranks.
+
+    Work per utterance is proportional to lx * (ly + 1) (gathered rows, lattice cells and patched
+    gradient rows).  Utterances are sorted by that weight and dealt in a snake (0..G-1, G-1..0, ...)
+    so that every rank gets the same COUNT (+-1) and nearly the same total weight.  Deterministic,
+    so every rank can compute the same plan from the same lengths without communication."""
+    lx = [int(v) for v in frames_lengths]
+    ly = [int(v) for v in labels_lengths]
+    assert len(lx) == len(ly) and world_size >= 1
+    order = sorted(range(len(lx)), key=lambda n: (-(lx[n] * (ly[n] + 1)), n))
+    plan: List[List[int]] = [[] for _ in range(world_size)]
+    for pos, n in enumerate(order):
+        lap, k = divmod(pos, world_size)
+        plan[k if lap % 2 == 0 else world_size - 1 - k].append(n)
+    return plan
+
+
+def shard_weights(frames_lengths, labels_lengths, plan) -> List[int]:
+    return [sum(int(frames_lengths[n]) * (int(labels_lengths[n]) + 1) for n in idx) for idx in plan]
+
+
+class _AllReduceSum(torch.autograd.Function):
+    """y = sum over ranks of x.  Each rank back-propagates only through its own term, so the
+    backward is the identity (every rank seeds the same global loss with the same grad)."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, group):
+        y = x.clone()
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad, None
+
+
+def all_reduce_sum(x: torch.Tensor, group=None) -> torch.Tensor:
+    return _AllReduceSum.apply(x, group)
+
+
+def reduce_costs(costs: torch.Tensor, frames_lengths: torch.Tensor, global_batch: int, reduction: Optional[str],
+                 average_frames: bool, group=None) -> torch.Tensor:
+    """Reduction of warp_ctct/__init__.py:138-147 over the global batch from this rank's costs."""
+    if average_frames:
+        costs = costs / frames_lengths
+    if reduction == "none" or reduction is None:
+        return costs  # per-utterance costs stay local
+    total = all_reduce_sum(costs.sum(), group)
+    if reduction == "mean":
+        return total / global_batch
+    return total
+
+
+def sharded_ctct_loss(log_probs: torch.Tensor, labels: torch.Tensor, frames_lengths: torch.Tensor,
+                      labels_lengths: torch.Tensor, global_batch: Optional[int] = None,
+                      reduction: Optional[str] = "mean", average_frames: bool = False, group=None) -> torch.Tensor:
+    """``ctct_loss`` on this rank's shard of a batch that is split across the process group.
+
+    ``log_probs`` etc. hold only the local utterances.  With ``reduction`` 'mean' or 'sum' the
+    returned scalar is the loss of the GLOBAL batch (identical on every rank) and its backward
+    writes d(global loss)/d(local log_probs); 'none' returns the local per-utterance costs.
+    ``global_batch`` defaults to the sum of local batch sizes when they are equal on all ranks."""
+    assert reduction is None or reduction in ("none", "mean", "sum")
+    assert log_probs.dim() == 4 and labels.dim() == 2
+    assert log_probs.size(2) == labels.size(1) + 1
+    assert log_probs.size(0) == labels.size(0) == frames_lengths.size(0) == labels_lengths.size(0)
+    _require_cuda(log_probs=log_probs, ys=labels, lx=frames_lengths, ly=labels_lengths)
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    if global_batch is None:
+        global_batch = log_probs.size(0) * world
+    enable_grad = log_probs.requires_grad and torch.is_grad_enabled()
+    if log_probs.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        log_probs = log_probs.float()
+    if not log_probs.is_contiguous():
+        log_probs = log_probs.contiguous()
+    costs = FusedCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
+                                enable_grad)
+    return reduce_costs(costs, frames_lengths, global_batch, reduction, average_frames, group)
