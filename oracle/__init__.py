@@ -202,20 +202,22 @@ def log_matmul_backward(grad_den, f, g, den, grad_f=None, grad_g=None, nthreads:
     return grad_f, grad_g
 
 
-def simple_loss(f, g, ys, lx, ly, normalized: bool = True, grad_out=None, nthreads: int = 0):
+def simple_loss(f, g, ys, lx, ly, normalized: bool = True, grad_out=None, nthreads: int = 0, dtype=np.float32):
     """ctct_simple_loss on host: returns (costs, grad_f (N,T,V), grad_g (N,U1,V)) as float64 arrays.
+    dtype float32 follows the reference's arithmetic (float32 denominator and tables); float64
+    evaluates the denominator and the lattice in double (the composed log-probs stay float32).
 
     Composition of warp_ctct/__init__.py:150-236: den = log_matmul, gathers, lattice on
     f+g-den, reductions, scatter back to the vocabulary, plus the log_matmul backward."""
     f, g, ys, lx, ly = _f32(f), _f32(g), _i32(ys), _i32(lx), _i32(ly)
     N, T, V = f.shape
     U1 = g.shape[1]
-    den = log_matmul(f, g, np.float32, nthreads) if normalized else None
+    den = log_matmul(f, g, dtype, nthreads).astype(np.float32) if normalized else None
     cf, cg = collect_separate(f, g, ys)
     g3 = compose_simple(cf, cg, den)
-    costs, grads3 = ctct_fwd(g3, ys, lx, ly, True, np.float32, nthreads)
+    costs, grads3 = ctct_fwd(g3, ys, lx, ly, True, dtype, nthreads)
     go = np.ones((N,), np.float32) if grad_out is None else _f32(grad_out)
-    grads3 = grads3 * go[:, None, None, None]
+    grads3 = (grads3 * go[:, None, None, None]).astype(np.float32)
     gcf, gcg, gden = simple_reduce(grads3, normalized)
     gf = np.zeros((N, T, V), np.float64)
     gg = np.zeros((N, U1, V), np.float64)

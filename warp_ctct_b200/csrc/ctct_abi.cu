@@ -52,19 +52,30 @@ int sm_count() {
     return sms > 0 ? sms : 148;
 }
 
-// contexts per thread (C) and threads per CTA for a given number of contexts: one context per
-// thread up to 1024 contexts, then 2, 4 or 8 per thread
+// Lattice slots (two per context) per thread and threads per CTA.  One warp handles 32 slots;
+// with several warps, 2 lanes (1 when a thread holds more than one slot) of every warp are halo
+// lanes, so a warp covers 30*C (31*C) slots.  One slot per thread up to 480 contexts.
 struct LatCfg {
     int C, threads;
 };
 bool lattice_config(int64_t U1, LatCfg *cfg) {
     if (U1 < 1 || U1 > 8192) return false;
-    int C = 1;
-    while (U1 > 1024 * C) C *= 2;
-    const int lanes = static_cast<int>((U1 + C - 1) / C);
-    cfg->C = C;
-    cfg->threads = ((lanes + 31) / 32) * 32;
-    return true;
+    const int64_t slots = 2 * U1;
+    if (slots <= 32) {
+        cfg->C = 1;
+        cfg->threads = 32;
+        return true;
+    }
+    for (int C = 1; C <= 32; C *= 2) {
+        const int per_warp = (C == 1 ? 30 : 31) * C;
+        const int64_t warps = (slots + per_warp - 1) / per_warp;
+        if (warps <= 32) {
+            cfg->C = C;
+            cfg->threads = static_cast<int>(warps) * 32;
+            return true;
+        }
+    }
+    return false;
 }
 
 size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
@@ -112,13 +123,17 @@ int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st) {
     int F = static_cast<int>((48 * 1024) / rowbytes);
     F = F < 1 ? 1 : (F > 16 ? 16 : F);
     a.F = F;
-    const size_t smem = 2 * static_cast<size_t>(F) * rowbytes + 2 * 32 * sizeof(float4);
+    if (F > 1) F &= ~1;  // even, so that the frame parity is the same in every chunk
+    a.F = F;
+    const size_t smem = 2 * static_cast<size_t>(F) * rowbytes + 5 * 33 * sizeof(float);
     if (smem > 220 * 1024) return CTCT_ERR_UNSUPPORTED;
     switch (cfg.C) {
     case 1: return launch_lattice_inst<1>(a, N, cfg.threads, smem, st);
     case 2: return launch_lattice_inst<2>(a, N, cfg.threads, smem, st);
     case 4: return launch_lattice_inst<4>(a, N, cfg.threads, smem, st);
     case 8: return launch_lattice_inst<8>(a, N, cfg.threads, smem, st);
+    case 16: return launch_lattice_inst<16>(a, N, cfg.threads, smem, st);
+    case 32: return launch_lattice_inst<32>(a, N, cfg.threads, smem, st);
     }
     return CTCT_ERR_UNSUPPORTED;
 }
@@ -185,7 +200,7 @@ LatticeArgs make_lattice_args(const WsLayout &w, char *ws, const int *ys, const 
     a.ys = ys;
     a.lx = lx;
     a.ly = ly;
-    a.TAB = reinterpret_cast<float4 *>(ws + w.TAB);
+    a.TAB = reinterpret_cast<float2 *>(ws + w.TAB);
     a.llf = reinterpret_cast<float *>(ws + w.LLF);
     a.lli = reinterpret_cast<int *>(ws + w.LLI);
     a.costs = costs;

@@ -20,12 +20,15 @@ namespace ctct {
 __device__ __forceinline__ float3 occupancies(const float4 *__restrict__ G, const float4 *__restrict__ TAB,
                                               const int *__restrict__ y, int64_t nt, int u, int U1, int Un, float lf,
                                               int li) {
+    // table record of a context: {label-state value, offset, blank-state value, offset}
     const float4 p = G[nt * U1 + u];
     const float4 av = TAB[(nt * 2 + 0) * U1 + u];
     const float4 bv = TAB[(nt * 2 + 1) * U1 + u];
-    const float aL = av.x, aB = av.y, bL = bv.x, bB = bv.y;
-    const int oA = __float_as_int(av.z);
-    const float c_same = static_cast<float>(oA + __float_as_int(bv.z) - li) - lf;
+    const float aL = av.x, aB = av.z, bL = bv.x, bB = bv.z;
+    // the blank slot of a live context is always written; a label slot shares its warp (and so
+    // its offset) whenever it exists
+    const int oA = __float_as_int(av.w);
+    const float c_same = static_cast<float>(oA + __float_as_int(bv.w) - li) - lf;
     // arcs leaving the blank state 2u: stay (blank), or emit label u
     float occ0 = ex2(aB + bB + p.x + c_same);
     float occ1 = 0.0f, occ2 = 0.0f;
@@ -36,7 +39,7 @@ __device__ __forceinline__ float3 occupancies(const float4 *__restrict__ G, cons
     }
     if (u < Un) {
         const float4 bn = TAB[(nt * 2 + 1) * U1 + u + 1];
-        const float c_next = static_cast<float>(oA + __float_as_int(bn.z) - li) - lf;
+        const float c_next = static_cast<float>(oA + __float_as_int(bn.y) - li) - lf;
         occ2 = ex2(aB + bn.x + p.z + c_next);
         if (u >= 1 && y[u] != y[u - 1]) occ2 += ex2(aL + bn.x + p.z + c_next);
     }
@@ -279,9 +282,9 @@ __global__ void __launch_bounds__(256) k_export_tables(const ExportArgs a) {
     double va = ninf, vb = ninf;
     if (t < Tn && u <= Un) {
         const float4 av = a.TAB[(nt * 2 + 0) * a.U1 + u], bv = a.TAB[(nt * 2 + 1) * a.U1 + u];
-        const float x = blank ? av.y : av.x, y = blank ? bv.y : bv.x;
-        if (x > NEG_TEST) va = (static_cast<double>(__float_as_int(av.z)) + x) * LN2;
-        if (y > NEG_TEST) vb = (static_cast<double>(__float_as_int(bv.z)) + y) * LN2;
+        const float x = blank ? av.z : av.x, y = blank ? bv.z : bv.x;
+        if (x > NEG_TEST) va = (static_cast<double>(__float_as_int(blank ? av.w : av.y)) + x) * LN2;
+        if (y > NEG_TEST) vb = (static_cast<double>(__float_as_int(blank ? bv.w : bv.y)) + y) * LN2;
     }
     a.alpha[nt * S + s] = va;
     a.beta_next[nt * S + s] = vb;

@@ -7,28 +7,25 @@
 //  * The recursion is time-synchronous: the state vector at frame t+1 depends only on the
 //    one at frame t.  In the reference's band storage a fixed frame is an anti-diagonal
 //    staircase; here a frame is simply one wavefront step.
-//  * One CTA per (utterance, direction), no waits between CTAs.  The 2U+1 lattice states
-//    live in REGISTERS, grouped by context u: a thread owns C consecutive contexts (C = 1 up
-//    to 1024 contexts) and for each the pair (label state 2u-1, blank state 2u).  A single
-//    warp is latency-bound on its own instruction stream, so the per-thread work is kept
-//    minimal and the contexts are spread over as many lanes as there are contexts; one step
-//    needs the neighbour's values through a warp shuffle, and across warps through shared
-//    memory and one CTA barrier per frame.
-//  * Every new state value is ONE log-sum-exp of values of the previous frame (the two- and
-//    three-way sums are taken directly, not chained), and the renormaliser of a frame is
-//    derived from the values the frame started with, so neither the neighbour exchange nor
-//    the renormalisation lengthens the frame-to-frame dependency chain.
+//  * One CTA per (utterance, direction), no waits between CTAs.  A lone warp issues about one
+//    instruction every five cycles, so a frame costs (instructions per frame) x 5 cycles and the
+//    design minimises exactly that count: ONE lattice state per thread, held in a register, and
+//    the same straight-line code for every state,
+//        new = lse3(own + p_stay, left + p_adv, skip ? left2 + p_adv : impossible),
+//    with the two neighbours taken by warp shuffles and, across warps, through shared memory
+//    and one CTA barrier per frame.  States sit in "slots": slot 2u = label state 2u-1 of
+//    context u, slot 2u+1 = blank state 2u; slot 0 is a dummy that stays impossible.
 //  * The three gathered log-probs per (frame, context) are one 16-byte record; they are
 //    staged through shared memory in chunks of F frames with cp.async, double buffered, so
 //    that the T dependent steps never wait on DRAM.
-//  * Arithmetic is in log2 units (ex2/lg2 are single MUFU instructions) and every thread keeps
-//    its values near zero by subtracting an INTEGER offset each frame; the offsets are carried
-//    exactly in int32.  The stored tables are therefore accurate to ~1e-6 regardless of T,
-//    where plain fp32 log-domain tables (values ~ -3000) carry ~1e-4.
+//  * Arithmetic is in log2 units (ex2/lg2 are single MUFU instructions).  Every RENORM frames a
+//    warp subtracts the rounded maximum of its 32 values (one redux.sync) and adds it to an
+//    exact int32 offset, so stored values stay within a few tens of zero whatever T is; plain
+//    fp32 log-domain tables (values ~ -3000, ulp 2.4e-4) cannot hold 1e-4 gradients.
 //
-// Table record (only written when a gradient is wanted), one float4 per (n, t, dir, u):
-//   dir 0: {alpha(t, 2u-1), alpha(t, 2u), offset, -}    dir 1: {beta(t+1, 2u-1), beta(t+1, 2u), offset, -}
-//   true value (log2 units) = stored + offset (offset is an int32 stored bit-for-bit).
+// Table record (only written when a gradient is wanted): float2 {value, int32 offset bits} per
+// (n, t, dir, slot); dir 0 = alpha(t), dir 1 = beta(t+1); true log2 value = value + offset.
+// Read per context as one float4 {label value, offset, blank value, offset}.
 #pragma once
 
 #include "common.cuh"
@@ -40,7 +37,7 @@ struct LatticeArgs {
     const int *ys;       // [N][U1-1]
     const int *lx;       // [N]
     const int *ly;       // [N]
-    float4 *TAB;         // [N][T][2][U1]
+    float2 *TAB;         // [N][T][2][2*U1]
     float *llf;          // [N][2]  fractional part of log2-likelihood from alpha / beta
     int *lli;            // [N][2]  integer part
     float *costs;        // [N]
@@ -48,64 +45,118 @@ struct LatticeArgs {
     int beta_only;       // 1: only the backward variable (no gradient wanted), no table stores
 };
 
-template <int C>
-__global__ void __launch_bounds__(1024) k_lattice(const LatticeArgs a) {
-    extern __shared__ __align__(16) float4 smem4[];
+constexpr int RENORM = 2;  // frames between renormalisations
+
+// C slots per thread (1 up to 480 contexts), DIR 0 = alpha / 1 = beta, MULTI = more than one warp.
+//
+// With more than one warp, H lanes of every warp are "halo" lanes (H = 2 for C = 1, else 1): they
+// hold copies of the neighbouring warp's two boundary slots, reloaded from shared memory at the
+// top of every frame, so that the neighbour values of all real lanes come from plain shuffles
+// with no per-lane fix-up.  A warp publishes its own two boundary slots after each step; one CTA
+// barrier per frame separates publishing from reloading.
+template <int C, int DIR, bool MULTI>
+__device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4) {
     constexpr unsigned FULL = 0xffffffffu;
+    constexpr int H = MULTI ? (C == 1 ? 2 : 1) : 0;
+    constexpr int REAL_LANES = 32 - H;
     const int n = blockIdx.x;
-    const int dir = a.beta_only ? 1 : static_cast<int>(blockIdx.y);
     const bool store = !a.beta_only;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int NT = blockDim.x, W = NT >> 5;
     const int U1 = a.U1, F = a.F, T = a.T;
-    const int U = U1 - 1;
+    const int U = U1 - 1, S2 = 2 * U1;  // number of slots
     const int Tn = max(0, min(a.lx[n], T));
     const int Un = max(0, min(a.ly[n], U));
-    const int u0 = tid * C;
-    const bool active = u0 <= Un;
+    // first slot of this thread; halo lanes mirror the neighbouring warp's numbering
+    const int j0 = (DIR == 0) ? (warp * REAL_LANES + lane - H) * C : (warp * REAL_LANES + lane) * C;
+    const bool halo = MULTI && ((DIR == 0) ? lane < H : lane >= REAL_LANES);
 
     float4 *buf0 = smem4;
     float4 *buf1 = smem4 + static_cast<size_t>(F) * U1;
-    float4 *xch = smem4 + 2 * static_cast<size_t>(F) * U1;  // [2][W] values handed to the next / previous warp
+    // exchange area after the two stage buffers: values [2 parities][W + 1][2], offsets [W + 1]
+    float *xs = reinterpret_cast<float *>(smem4 + 2 * static_cast<size_t>(F) * U1);
+    int *xo = reinterpret_cast<int *>(xs + 4 * (W + 1));
+    // alpha: warp w publishes into entry w+1 and reads entry w (entry 0 stays impossible);
+    // beta : warp w publishes into entry w and reads entry w+1 (entry W stays impossible)
+    const int e_pub = (DIR == 0) ? warp + 1 : warp;
+    const int e_in = (DIR == 0) ? warp : warp + 1;
 
-    bool dskip[C], labok[C];
-    int uidx[C];
+    // per-slot constants: word offsets of the emissions inside a staged row, masks
+    int ofs_s[C], ofs_a[C];
+    float mask_a[C];
+    bool skip[C], real[C];
     {
         const int *y = a.ys + static_cast<int64_t>(n) * U;
 #pragma unroll
         for (int c = 0; c < C; ++c) {
-            const int u = u0 + c;
-            uidx[c] = min(u, U1 - 1);
-            labok[c] = u < Un;
-            dskip[c] = false;
-            if (u >= 1 && u < Un) dskip[c] = y[u] != y[u - 1];
+            const int jr = j0 + c;
+            const int j = min(max(jr, 0), S2 - 1);
+            const int u = j >> 1;
+            const bool blank = j & 1;
+            real[c] = !halo && jr >= 1 && jr < S2 && u <= Un;
+            ofs_s[c] = 4 * u + (blank ? 0 : 1);
+            if (DIR == 0) {
+                // blank 2u  : stay p0[u], from the label state of u      p0[u]
+                // label 2u-1: stay p1[u], from blank / label of u-1      p2[u-1]
+                ofs_a[c] = blank ? 4 * u : 4 * max(u - 1, 0) + 2;
+                mask_a[c] = real[c] ? 0.0f : NEG;
+                skip[c] = real[c] && !blank && u >= 2 && y[u - 1] != y[u - 2];
+            } else {
+                // blank 2u  : stay p0[u], to the label of u+1 p2[u] (if it exists)
+                // label 2u-1: stay p1[u], to the blank of u   p0[u], skip to the label of u+1 p2[u]
+                ofs_a[c] = 4 * u + (blank ? 2 : 0);
+                mask_a[c] = (real[c] && (!blank || u < Un)) ? 0.0f : NEG;
+                skip[c] = real[c] && !blank && u < Un && y[u] != y[u - 1];
+            }
         }
     }
 
     const int64_t rowbase = static_cast<int64_t>(n) * T;
     const float4 *Gn = a.G + rowbase * U1;
 
-    float L[C], Bk[C];
+    float x[C];
     int off = 0;
 #pragma unroll
     for (int c = 0; c < C; ++c) {
-        L[c] = NEG;
-        Bk[c] = NEG;
-    }
-    if (dir == 0) {
-        if (tid == 0) Bk[0] = 0.0f;
-    } else {
-#pragma unroll
-        for (int c = 0; c < C; ++c)
-            if (u0 + c == Un) {
-                Bk[c] = 0.0f;
-                if (Un >= 1) L[c] = 0.0f;
+        const int j = j0 + c;
+        x[c] = NEG;
+        if (!halo) {
+            if (DIR == 0) {
+                if (j == 1) x[c] = 0.0f;
+            } else {
+                if (j == 2 * Un + 1 || (j == 2 * Un && Un >= 1)) x[c] = 0.0f;
             }
+        }
     }
+    if (MULTI) {
+        for (int i = tid; i < 4 * (W + 1); i += NT) xs[i] = NEG;
+        for (int i = tid; i < W + 1; i += NT) xo[i] = 0;
+        __syncthreads();
+        // publish the starting values so that the first halo load sees them
+        if (DIR == 0) {
+            if (C == 1) {
+                if (lane >= 30) xs[(0 * (W + 1) + e_pub) * 2 + lane - 30] = x[0];
+            } else if (lane == 31) {
+                xs[(0 * (W + 1) + e_pub) * 2 + 0] = x[C >= 2 ? C - 2 : 0];
+                xs[(0 * (W + 1) + e_pub) * 2 + 1] = x[C - 1];
+            }
+        } else {
+            if (C == 1) {
+                if (lane < 2) xs[(0 * (W + 1) + e_pub) * 2 + lane] = x[0];
+            } else if (lane == 0) {
+                xs[(0 * (W + 1) + e_pub) * 2 + 0] = x[0];
+                xs[(0 * (W + 1) + e_pub) * 2 + 1] = x[C >= 2 ? 1 : 0];
+            }
+        }
+        __syncthreads();
+    }
+    float adj = 0.0f;        // neighbour warp's offset minus ours
+    bool untouched = true;   // no state of this warp reachable yet (as of the last renormalisation)
+    bool refresh = false;    // offsets changed in the previous frame: re-read the neighbour's
 
     const int nchunks = (Tn + F - 1) / F;
     auto chunk_range = [&](int c, int &lo, int &hi) {
-        if (dir == 0) {
+        if (DIR == 0) {
             lo = c * F;
             hi = min(Tn, lo + F);
         } else {
@@ -121,14 +172,33 @@ __global__ void __launch_bounds__(1024) k_lattice(const LatticeArgs a) {
         for (int v = tid; v < nvec; v += NT) cp_async16(dst + v, src + v);
         cp_async_commit();
     };
-    auto sync = [&]() {
-        if (W == 1)
-            __syncwarp();
-        else
-            __syncthreads();
+    // reload the halo lanes from what the neighbouring warp published in buffer `par`
+    auto load_halo = [&](int par) {
+        if (!MULTI) return;
+        if (refresh) {
+            const int offp = xo[e_in];
+            if (untouched) off = offp;  // adopt the neighbour's scale until something arrives
+            adj = static_cast<float>(offp - off);
+        }
+        const float *in = xs + (par * (W + 1) + e_in) * 2;
+        if (DIR == 0) {
+            if (C == 1) {
+                if (lane < 2) x[0] = in[lane] + adj;
+            } else if (lane == 0) {
+                x[C >= 2 ? C - 2 : 0] = in[0] + adj;
+                x[C - 1] = in[1] + adj;
+            }
+        } else {
+            if (C == 1) {
+                if (lane >= 30) x[0] = in[lane - 30] + adj;
+            } else if (lane == 31) {
+                x[0] = in[0] + adj;
+                x[C >= 2 ? 1 : 0] = in[1] + adj;
+            }
+        }
     };
 
-    int parity = 0;
+    int frame = 0;
     if (nchunks > 0) issue(0, buf0);
     for (int c = 0; c < nchunks; ++c) {
         const float4 *cur = (c & 1) ? buf1 : buf0;
@@ -138,128 +208,157 @@ __global__ void __launch_bounds__(1024) k_lattice(const LatticeArgs a) {
         } else {
             cp_async_wait<0>();
         }
-        sync();
+        if (MULTI)
+            __syncthreads();
+        else
+            __syncwarp();
         int lo, hi;
         chunk_range(c, lo, hi);
         const int nf = hi - lo;
-        const int tstep = (dir == 0) ? 1 : -1;
-        int t = (dir == 0) ? lo : hi - 1;
-        const float4 *row = cur + static_cast<int64_t>(t - lo) * U1;
-        float4 *tr = a.TAB + ((rowbase + t) * 2 + dir) * U1 + u0;
-        for (int f = 0; f < nf; ++f, t += tstep, row += tstep * U1, tr += tstep * 2 * U1) {
-            if (store && active) {
+        constexpr int tstep = (DIR == 0) ? 1 : -1;
+        int t = (DIR == 0) ? lo : hi - 1;
+        const float *row = reinterpret_cast<const float *>(cur + static_cast<int64_t>(t - lo) * U1);
+        float2 *tr = a.TAB + ((rowbase + t) * 2 + DIR) * S2 + j0;
+#pragma unroll 2
+        for (int f = 0; f < nf; ++f, ++frame, t += tstep, row += tstep * 4 * U1, tr += tstep * 2 * S2) {
+            const int par = frame & 1;
+            load_halo(par);  // values published at the end of the previous frame (buffer par)
+            // ---- renormalise (warp-uniform), every RENORM frames: subtract the rounded warp maximum
+            const bool renorm = (frame % RENORM) == 0;
+            refresh = false;
+            if (renorm) {
+                int ki = __float2int_rn(x[0]);
+#pragma unroll
+                for (int cc = 1; cc < C; ++cc) ki = max(ki, __float2int_rn(x[cc]));
+                ki = __reduce_max_sync(FULL, ki);
+                untouched = ki < -(1 << 30);
+                if (!untouched) {
+                    const float k = static_cast<float>(ki);
+#pragma unroll
+                    for (int cc = 0; cc < C; ++cc) x[cc] -= k;
+                    off += ki;
+                }
+                refresh = true;
+            }
+            if (store) {
 #pragma unroll
                 for (int cc = 0; cc < C; ++cc)
-                    if (u0 + cc < U1) tr[cc] = make_float4(L[cc], Bk[cc], __int_as_float(off), 0.0f);
+                    if (real[cc]) tr[cc] = make_float2(x[cc], __int_as_float(off));
             }
 
-            float4 p[C];
-#pragma unroll
-            for (int cc = 0; cc < C; ++cc) p[cc] = row[uidx[cc]];
-
-            // Renormaliser of this frame, from the values the frame starts with (off the
-            // dependency chain: it is only needed for the final subtraction).
-            float m = NEG;
-#pragma unroll
-            for (int cc = 0; cc < C; ++cc) m = fmaxf(m, fmaxf(L[cc], Bk[cc]));
-            const bool untouched = !(m > NEG_TEST);
-            const float k = untouched ? 0.0f : rintf(m);
-
-            float nL[C], nB[C];
-            if (dir == 0) {
-                // alpha(t+1) from alpha(t).  tB / tL: what context u sends into label state 2u+1,
-                // from its blank state 2u and, when labels u-1 and u differ, from its label
-                // state 2u-1 (gather.cu:131-148 in band coordinates).
-                float tB[C], tL[C];
-#pragma unroll
-                for (int cc = 0; cc < C; ++cc) {
-                    tB[cc] = labok[cc] ? p[cc].z + Bk[cc] : NEG;
-                    tL[cc] = dskip[cc] ? p[cc].z + L[cc] : NEG;
-                }
-                float inB = __shfl_up_sync(FULL, tB[C - 1], 1);
-                float inL = __shfl_up_sync(FULL, tL[C - 1], 1);
-                int oin = __shfl_up_sync(FULL, off, 1);
-                if (W > 1) {
-                    if (lane == 31) xch[parity * W + warp] = make_float4(tB[C - 1], tL[C - 1], __int_as_float(off), 0.0f);
-                    __syncthreads();
-                    if (lane == 0 && warp > 0) {
-                        const float4 x = xch[parity * W + warp - 1];
-                        inB = x.x;
-                        inL = x.y;
-                        oin = __float_as_int(x.z);
-                    }
-                    parity ^= 1;
-                }
-                if (tid == 0) {
-                    inB = NEG;
-                    inL = NEG;
-                }
-                // a thread none of whose states has been reached yet adopts its neighbour's
-                // scale, so the first value it receives is small in magnitude
-                if (untouched && (inB > NEG_TEST || inL > NEG_TEST)) off = oin;
-                const float adj = static_cast<float>(oin - off);
-                inB = (inB > NEG_TEST) ? inB + adj : NEG;
-                inL = (inL > NEG_TEST) ? inL + adj : NEG;
-#pragma unroll
-                for (int cc = 0; cc < C; ++cc) {
-                    const float b1 = (cc == 0) ? inB : tB[cc == 0 ? 0 : cc - 1];
-                    const float c1 = (cc == 0) ? inL : tL[cc == 0 ? 0 : cc - 1];
-                    nL[cc] = lse3(L[cc] + p[cc].y, b1, c1);
-                    nB[cc] = p[cc].x + lse2(Bk[cc], L[cc]);
+            // ---- neighbours: slot j-1, j-2 (alpha) or j+1, j+2 (beta)
+            float n1, n2;  // for the first (alpha) / last (beta) slot of this thread
+            if (DIR == 0) {
+                n1 = __shfl_up_sync(FULL, x[C - 1], 1);
+                n2 = (C >= 2) ? __shfl_up_sync(FULL, x[C >= 2 ? C - 2 : 0], 1) : __shfl_up_sync(FULL, x[0], 2);
+                if (!MULTI) {
+                    if (lane == 0) n1 = NEG;
+                    if (lane == 0 || (C == 1 && lane == 1)) n2 = NEG;
                 }
             } else {
-                // beta(t) from beta(t+1) (gather.cu:222-271 in band coordinates).
-                float Lin = __shfl_down_sync(FULL, L[0], 1);
-                int oin = __shfl_down_sync(FULL, off, 1);
-                if (W > 1) {
-                    if (lane == 0) xch[parity * W + warp] = make_float4(L[0], 0.0f, __int_as_float(off), 0.0f);
-                    __syncthreads();
-                    if (lane == 31 && warp + 1 < W) {
-                        const float4 x = xch[parity * W + warp + 1];
-                        Lin = x.x;
-                        oin = __float_as_int(x.z);
-                    }
-                    parity ^= 1;
+                n1 = __shfl_down_sync(FULL, x[0], 1);
+                n2 = (C >= 2) ? __shfl_down_sync(FULL, x[C >= 2 ? 1 : 0], 1) : __shfl_down_sync(FULL, x[0], 2);
+                if (!MULTI) {
+                    if (lane == 31) n1 = NEG;
+                    if (lane == 31 || (C == 1 && lane == 30)) n2 = NEG;
                 }
-                if (tid == NT - 1) Lin = NEG;
-                if (untouched && Lin > NEG_TEST) off = oin;
-                Lin = (Lin > NEG_TEST) ? Lin + static_cast<float>(oin - off) : NEG;
-#pragma unroll
-                for (int cc = 0; cc < C; ++cc) {
-                    const float ln = (cc == C - 1) ? Lin : L[cc == C - 1 ? cc : cc + 1];
-                    const float X = p[cc].x + Bk[cc];                   // emit blank, go to / stay in 2u
-                    const float Y = labok[cc] ? p[cc].z + ln : NEG;     // emit label u, go to 2u+1
-                    nB[cc] = lse2(X, Y);
-                    nL[cc] = lse3(p[cc].y + L[cc], X, dskip[cc] ? Y : NEG);
-                }
-                if (tid == 0) nL[0] = NEG;  // context 0 has no label state
             }
 
-            // keep this thread's values near zero; the integer offset carries the rest exactly
+            // ---- one step of the recursion for every slot of this thread
+            float nx[C];
 #pragma unroll
             for (int cc = 0; cc < C; ++cc) {
-                L[cc] = nL[cc] - k;
-                Bk[cc] = nB[cc] - k;
+                float v1, v2;
+                if (DIR == 0) {
+                    v1 = (cc >= 1) ? x[cc >= 1 ? cc - 1 : 0] : n1;
+                    v2 = (cc >= 2) ? x[cc >= 2 ? cc - 2 : 0] : ((cc == 1) ? n1 : n2);
+                } else {
+                    v1 = (cc + 1 < C) ? x[cc + 1 < C ? cc + 1 : 0] : n1;
+                    v2 = (cc + 2 < C) ? x[cc + 2 < C ? cc + 2 : 0] : ((cc + 2 == C) ? n1 : n2);
+                }
+                const float ps = row[ofs_s[cc]];
+                const float pa = row[ofs_a[cc]] + mask_a[cc];
+                float pk = pa;
+                if (DIR == 1) pk = row[(ofs_s[cc] & ~3) + 2];  // next-label emission of the same context
+                const float t3 = skip[cc] ? v2 + pk : NEG;
+                nx[cc] = lse3(x[cc] + ps, v1 + pa, t3);
             }
-            off += static_cast<int>(k);
+#pragma unroll
+            for (int cc = 0; cc < C; ++cc) x[cc] = nx[cc];
+
+            // ---- publish this warp's boundary slots (buffer par^1) and, after a renormalisation,
+            // its offset; the barrier orders them before the neighbour's reload
+            if (MULTI) {
+                float *out = xs + ((par ^ 1) * (W + 1) + e_pub) * 2;
+                if (DIR == 0) {
+                    if (C == 1) {
+                        if (lane >= 30) out[lane - 30] = x[0];
+                    } else if (lane == 31) {
+                        out[0] = x[C >= 2 ? C - 2 : 0];
+                        out[1] = x[C - 1];
+                    }
+                    if (renorm && lane == 31) xo[e_pub] = off;
+                } else {
+                    if (C == 1) {
+                        if (lane < 2) out[lane] = x[0];
+                    } else if (lane == 0) {
+                        out[0] = x[0];
+                        out[1] = x[C >= 2 ? 1 : 0];
+                    }
+                    if (renorm && lane == 0) xo[e_pub] = off;
+                }
+                __syncthreads();
+            }
         }
-        sync();
+        if (MULTI)
+            __syncthreads();
+        else
+            __syncwarp();
     }
 
-    if (dir == 0) {
+    // ---- log-likelihood
+    if (DIR == 0) {
+        // alpha(T, 2U-1) and alpha(T, 2U) live in slots 2Un and 2Un+1: same thread (C even) or
+        // adjacent real lanes of one warp (warps start on even slots)
+        float left[C];
+        const float prev = __shfl_up_sync(FULL, x[C - 1], 1);
+#pragma unroll
+        for (int cc = 0; cc < C; ++cc) left[cc] = (cc >= 1) ? x[cc >= 1 ? cc - 1 : 0] : prev;
 #pragma unroll
         for (int cc = 0; cc < C; ++cc)
-            if (u0 + cc == Un) {
-                a.llf[n * 2 + 0] = lse2(Bk[cc], L[cc]);
+            if (!halo && j0 + cc == 2 * Un + 1) {
+                a.llf[n * 2 + 0] = lse2(x[cc], (j0 + cc == 1) ? NEG : left[cc]);
                 a.lli[n * 2 + 0] = off;
             }
-    } else if (tid == 0) {
-        a.llf[n * 2 + 1] = Bk[0];
-        a.lli[n * 2 + 1] = off;
-        const float frac = Bk[0];
-        float cost = __int_as_float(0x7f800000);  // no alignment exists
-        if (frac > NEG_TEST) cost = static_cast<float>(-(static_cast<double>(off) + static_cast<double>(frac)) * LN2);
-        a.costs[n] = cost;
+    } else {
+#pragma unroll
+        for (int cc = 0; cc < C; ++cc)
+            if (!halo && j0 + cc == 1) {
+                const float frac = x[cc];
+                a.llf[n * 2 + 1] = frac;
+                a.lli[n * 2 + 1] = off;
+                float cost = __int_as_float(0x7f800000);  // no alignment exists
+                if (frac > NEG_TEST) cost = static_cast<float>(-(static_cast<double>(off) + static_cast<double>(frac)) * LN2);
+                a.costs[n] = cost;
+            }
+    }
+}
+
+template <int C>
+__global__ void __launch_bounds__(1024) k_lattice(const LatticeArgs a) {
+    extern __shared__ __align__(16) float4 smem4[];
+    const int dir = a.beta_only ? 1 : static_cast<int>(blockIdx.y);
+    const bool multi = blockDim.x > 32;
+    if (dir == 0) {
+        if (multi)
+            lattice_run<C, 0, true>(a, smem4);
+        else
+            lattice_run<C, 0, false>(a, smem4);
+    } else {
+        if (multi)
+            lattice_run<C, 1, true>(a, smem4);
+        else
+            lattice_run<C, 1, false>(a, smem4);
     }
 }
 
