@@ -27,6 +27,7 @@ extern "C" {
 #define CTCT_ERR_WORKSPACE (-2)  /* workspace missing, too small or misaligned          */
 #define CTCT_ERR_LAUNCH (-3)     /* CUDA reported a launch / configuration error        */
 #define CTCT_ERR_UNSUPPORTED (-4)/* size outside what the kernels were built for        */
+#define CTCT_ERR_STATIC_SCRATCH (-5) /* problem needs more scratch than the built-in buffer holds */
 
 /* element type of the joint tensor and of the dense gradient */
 #define CTCT_F32 0
@@ -62,6 +63,36 @@ int ctct_b200_loss_forward(const void *log_probs, int dtype, const int32_t *ys, 
                            const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
                            int want_grad, float *costs, float *grads3, void *workspace,
                            size_t workspace_bytes, void *stream);
+
+/*
+ * ctct_b200_loss_forward without a caller-provided workspace.  (No counterpart in the
+ * reference: its host layer always allocates with torch.)
+ *
+ * For callers that are not allowed to allocate device memory at the time of the call: a
+ * plug-in inside a host application that hands out all device memory at start-up and forbids
+ * cudaMalloc afterwards, or a latency-critical loop in which the implicit device-wide
+ * synchronisation of an allocation is not acceptable, and that have no caching allocator of
+ * their own to take a workspace from.  Inputs and outputs are still the caller's buffers.
+ *
+ * The scratch lives in a fixed array inside the library's device image,
+ * CTCT_NOALLOC_SCRATCH_BYTES (32 MiB) large; every GPU that loads the library carries that array
+ * until the process exits.  A problem whose ctct_b200_workspace_bytes(N,T,U1,want_grad)
+ * exceeds it is rejected with CTCT_ERR_STATIC_SCRATCH before anything is launched (the first
+ * benchmark shape, N=32,T=256,U1=65 with gradient, needs 24.4 MiB).  The function calls no
+ * cudaMalloc/cudaFree and no allocating library routine.
+ *
+ * The first call on each device looks up the array's device address once (with that device
+ * current) and caches it; make that first call outside any stream capture.
+ * All calls share the one array and it keeps whatever the previous call left there; the
+ * kernels write every scratch location before they read it, so nothing has to be cleared.
+ * Two calls that overlap on the same GPU (different streams or host threads) race on the
+ * array: serialise them, or give all but one of them the workspace variant.
+ * Same arguments and results as ctct_b200_loss_forward otherwise.
+ */
+#define CTCT_NOALLOC_SCRATCH_BYTES (32u << 20)
+int ctct_b200_loss_forward_noalloc(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx,
+                                   const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
+                                   int want_grad, float *costs, float *grads3, void *stream);
 
 /*
  * Dense gradient: dense[n,t,u,:] = 0 except the blank column and the columns of

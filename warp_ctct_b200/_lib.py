@@ -27,6 +27,7 @@ SIGNATURES = {
     "ctct_b200_grads3_elems": (_sz, [_i64, _i64, _i64]),
     "ctct_b200_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "ctct_b200_loss_forward": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
+    "ctct_b200_loss_forward_noalloc": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp]),
     "ctct_b200_loss_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "ctct_b200_gather": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "ctct_b200_gathered_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),

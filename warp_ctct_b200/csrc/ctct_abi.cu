@@ -275,6 +275,9 @@ const char *ctct_b200_strerror(int code) {
     case CTCT_ERR_WORKSPACE: return "workspace missing, too small or not 256-byte aligned";
     case CTCT_ERR_LAUNCH: return g_last_cuda_error[0] ? g_last_cuda_error : "CUDA launch failed";
     case CTCT_ERR_UNSUPPORTED: return "size not supported by the kernels";
+    case CTCT_ERR_STATIC_SCRATCH:
+        return "problem needs more scratch than the 32 MiB built into the library; use ctct_b200_loss_forward "
+               "with a caller-provided workspace";
     }
     return "unknown error";
 }
@@ -591,3 +594,39 @@ int ctct_b200_profile_read(float *ms, int *kind, int capacity) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Forward without a caller-provided workspace: the scratch is a fixed array in the device image.
+// In host code `g_noalloc_scratch` is only a handle for the symbol, never a device address; the
+// address the kernels get comes from cudaGetSymbolAddress, looked up once per device.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CTCT_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void *g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+}  // namespace
+
+extern "C" int ctct_b200_loss_forward_noalloc(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx,
+                                              const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
+                                              int want_grad, float *costs, float *grads3, void *stream) {
+    if (!dims_ok(N, T, U1)) return CTCT_ERR_ARG;
+    if (N == 0) return CTCT_OK;
+    WsLayout w;
+    if (!ws_layout(N, T, U1, want_grad, &w)) return CTCT_ERR_UNSUPPORTED;
+    if (w.total > CTCT_NOALLOC_SCRATCH_BYTES) return CTCT_ERR_STATIC_SCRATCH;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return check_launch("noalloc device");
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_ptr[dev]) {
+            void *p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return check_launch("noalloc symbol address");
+            g_noalloc_ptr[dev] = p;
+        }
+        scratch = g_noalloc_ptr[dev];
+    }
+    return ctct_b200_loss_forward(log_probs, dtype, ys, lx, ly, N, T, U1, V, want_grad, costs, grads3, scratch,
+                                  CTCT_NOALLOC_SCRATCH_BYTES, stream);
+}
