@@ -108,6 +108,25 @@ int ctct_b200_loss_backward(const float *grads3, const float *grad_out, const in
                             int64_t V, int dtype, void *dense, void *stream);
 
 /*
+ * The same pair with the reduction of warp_ctct/__init__.py:138-147 folded in, so that no
+ * separate reduction kernels run:  loss = sum_n costs[n] * w[n],
+ *   w[n] = (average_frames ? 1/lx[n] : 1) * (reduction == 2 ? 1/norm : 1),
+ *   reduction: 1 = 'sum', 2 = 'mean' (norm = batch size; a sharded caller passes the global batch).
+ * Forward writes costs (N) as before and the scalar *loss (deterministic summation order).
+ * Backward takes the gradient of that scalar, grad_loss (ONE float on the device), and scales
+ * utterance n by grad_loss[0] * w[n].
+ */
+int ctct_b200_loss_forward_reduced(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx,
+                                   const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
+                                   int want_grad, int reduction, int average_frames, float norm,
+                                   float *costs, float *loss, float *grads3, void *workspace,
+                                   size_t workspace_bytes, void *stream);
+int ctct_b200_loss_backward_reduced(const float *grads3, const float *grad_loss, int reduction,
+                                    int average_frames, float norm, const int32_t *ys, const int32_t *lx,
+                                    const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int dtype,
+                                    void *dense, void *stream);
+
+/*
  * The gather alone, in the reference's layout: gathered[n,t,u,0..2] =
  * log_probs[n,t,u,{0, ys[n,u-1], ys[n,u]}] converted to float32 (slots without a
  * label read column 0).  Replaces collect_units (ref_ctct.py:223-230) /

@@ -74,6 +74,49 @@ class FusedCTCTLoss(torch.autograd.Function):
         return dense, None, None, None, None
 
 
+class FusedCTCTLossReduced(torch.autograd.Function):
+    """FusedCTCTLoss with the reduction of warp_ctct/__init__.py:138-147 folded into the kernels:
+    returns the 0-dim loss  sum_n costs[n] * w[n],  w[n] = (average_frames ? 1/lx[n] : 1) *
+    (mean ? 1/norm : 1).  No separate sum / divide / expand kernels run in either direction."""
+
+    @staticmethod
+    def forward(ctx, log_probs: T, labels: T, lx: T, ly: T, requires_grad: bool, mean: bool, average_frames: bool,
+                norm: float):
+        N, Tm, U1, V = log_probs.shape
+        dev = log_probs.device
+        lib = _lib.lib()
+        red = 2 if mean else 1
+        out = torch.empty((N + 1,), dtype=torch.float32, device=dev)  # [loss, costs...]
+        with torch.cuda.device(dev):
+            ws = _lib.workspace(N, Tm, U1, requires_grad, dev)
+            grads3 = None
+            if requires_grad:
+                grads3 = torch.empty((lib.ctct_b200_grads3_elems(N, Tm, U1),), dtype=torch.float32, device=dev)
+            rc = lib.ctct_b200_loss_forward_reduced(
+                _lib.ptr(log_probs), _lib.dtype_code(log_probs.dtype), _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
+                N, Tm, U1, V, int(requires_grad), red, int(bool(average_frames)), float(norm),
+                out.data_ptr() + 4, out.data_ptr(), _lib.ptr(grads3), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+        _lib.check(rc, "ctct_b200_loss_forward_reduced")
+        if requires_grad:
+            ctx.save_for_backward(grads3, labels, lx, ly)
+            ctx.meta = (N, Tm, U1, V, log_probs.dtype, red, bool(average_frames), float(norm))
+        return out[0]
+
+    @staticmethod
+    def backward(ctx, grad_loss: T):
+        grads3, labels, lx, ly = ctx.saved_tensors
+        N, Tm, U1, V, dtype, red, avg, norm = ctx.meta
+        dev = grads3.device
+        go = grad_loss.to(torch.float32).contiguous()
+        dense = torch.empty((N, Tm, U1, V), dtype=dtype, device=dev)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().ctct_b200_loss_backward_reduced(
+                _lib.ptr(grads3), _lib.ptr(go), red, int(avg), norm, _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
+                N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
+        _lib.check(rc, "ctct_b200_loss_backward_reduced")
+        return dense, None, None, None, None, None, None, None
+
+
 def ctct_loss_fwd(log_probs: T, ys: T, lx: T, ly: T, requires_grad: bool):
     """Extension-level entry point of the reference, ``_C.ctct_loss_fwd`` (csrc/binding.cpp:31-100):
     gathered float32 log-probs (N,T,U+1,3) -> (costs, grads); ``grads`` is ``costs`` when no
@@ -174,6 +217,10 @@ def ctct_loss(log_probs: torch.FloatTensor,
         log_probs = log_probs.float()
     if not log_probs.is_contiguous():
         log_probs = log_probs.contiguous()
+    if reduction in ("mean", "sum") and log_probs.size(0) > 0:
+        return FusedCTCTLossReduced.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
+                                          enable_grad, reduction == "mean", bool(average_frames),
+                                          float(log_probs.size(0)))
     costs = FusedCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
                                 enable_grad)
     return _reduce(costs, frames_lengths, reduction, average_frames)

@@ -173,9 +173,21 @@ int launch_gather(const void *lp, int dtype, const int *ys, const int *lx, const
 }
 
 int launch_fill_grad(const WsLayout &w, char *ws, const int *ys, const int *lx, const int *ly, float *out,
-                     int ref_layout, int64_t N, int64_t T, int64_t U1, cudaStream_t st) {
-    if (N == 0 || T == 0) return CTCT_OK;
+                     int ref_layout, int64_t N, int64_t T, int64_t U1, cudaStream_t st, const float *costs = nullptr,
+                     float *loss_out = nullptr, ReduceSpec red = ReduceSpec{0, 0, 1.0f}) {
+    if (N == 0) return CTCT_OK;
+    if (T == 0) {
+        if (loss_out) {
+            k_reduce_costs<<<1, 256, 0, st>>>(costs, lx, (int)N, red, loss_out);
+            return check_launch("reduce_costs");
+        }
+        return CTCT_OK;
+    }
     GradArgs g;
+    g.costs = costs;
+    g.loss_out = loss_out;
+    g.N = (int)N;
+    g.red = red;
     g.G = reinterpret_cast<const float4 *>(ws + w.G);
     g.TAB = reinterpret_cast<const float4 *>(ws + w.TAB);
     g.llf = reinterpret_cast<const float *>(ws + w.LLF);
@@ -262,6 +274,53 @@ int launch_logmm_bwd(const LogmmBwdArgs &a, int64_t B, cudaStream_t st) {
     return CTCT_ERR_UNSUPPORTED;
 }
 
+int dense_backward(DenseArgs a, int64_t N, int dtype, void *stream) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
+    cudaEvent_t *slot = prof_slot(1);
+    prof_mark(slot, 0, st);
+    int rc = CTCT_ERR_ARG;
+    switch (dtype) {
+    case CTCT_F32: rc = launch_dense_t<float>(a, N, st); break;
+    case CTCT_F16: rc = launch_dense_t<__half>(a, N, st); break;
+    case CTCT_BF16: rc = launch_dense_t<__nv_bfloat16>(a, N, st); break;
+    }
+    prof_mark(slot, 1, st);
+    return rc;
+}
+
+// gather -> lattice -> occupancy gradient (+ optional reduction of the costs into *loss_out)
+int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
+                 int64_t T, int64_t U1, int64_t V, int want_grad, float *costs, float *grads3, void *workspace,
+                 size_t workspace_bytes, void *stream, float *loss_out, ReduceSpec red) {
+    if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
+    if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
+    if (N == 0) return CTCT_OK;
+    if (!log_probs || !lx || !ly || !costs || (U1 > 1 && !ys) || (want_grad && !grads3)) return CTCT_ERR_ARG;
+    WsLayout w;
+    if (!ws_layout(N, T, U1, want_grad, &w)) return CTCT_ERR_UNSUPPORTED;
+    if (!workspace || workspace_bytes < w.total || reinterpret_cast<uintptr_t>(workspace) % 256) return CTCT_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char *ws = static_cast<char *>(workspace);
+
+    cudaEvent_t *slot = prof_slot(0);
+    prof_mark(slot, 0, st);
+    int rc = launch_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float *>(ws + w.G), N, T, U1, V, true, 1, st);
+    if (rc) return rc;
+    prof_mark(slot, 1, st);
+    rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st);
+    if (rc) return rc;
+    prof_mark(slot, 2, st);
+    if (want_grad) {
+        rc = launch_fill_grad(w, ws, ys, lx, ly, grads3, 0, N, T, U1, st, costs, loss_out, red);
+    } else if (loss_out) {
+        k_reduce_costs<<<1, 256, 0, st>>>(costs, lx, (int)N, red, loss_out);
+        rc = check_launch("reduce_costs");
+    }
+    prof_mark(slot, 3, st);
+    return rc;
+}
+
 }  // namespace
 
 extern "C" {
@@ -296,27 +355,41 @@ size_t ctct_b200_workspace_bytes(int64_t N, int64_t T, int64_t U1, int want_grad
 int ctct_b200_loss_forward(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx,
                            const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int want_grad,
                            float *costs, float *grads3, void *workspace, size_t workspace_bytes, void *stream) {
-    if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
-    if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
-    if (N == 0) return CTCT_OK;
-    if (!log_probs || !lx || !ly || !costs || (U1 > 1 && !ys) || (want_grad && !grads3)) return CTCT_ERR_ARG;
-    WsLayout w;
-    if (!ws_layout(N, T, U1, want_grad, &w)) return CTCT_ERR_UNSUPPORTED;
-    if (!workspace || workspace_bytes < w.total || reinterpret_cast<uintptr_t>(workspace) % 256) return CTCT_ERR_WORKSPACE;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    char *ws = static_cast<char *>(workspace);
+    return forward_impl(log_probs, dtype, ys, lx, ly, N, T, U1, V, want_grad, costs, grads3, workspace, workspace_bytes,
+                        stream, nullptr, ReduceSpec{0, 0, 1.0f});
+}
 
-    cudaEvent_t *slot = prof_slot(0);
-    prof_mark(slot, 0, st);
-    int rc = launch_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float *>(ws + w.G), N, T, U1, V, true, 1, st);
-    if (rc) return rc;
-    prof_mark(slot, 1, st);
-    rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st);
-    if (rc) return rc;
-    prof_mark(slot, 2, st);
-    if (want_grad) rc = launch_fill_grad(w, ws, ys, lx, ly, grads3, 0, N, T, U1, st);
-    prof_mark(slot, 3, st);
-    return rc;
+int ctct_b200_loss_forward_reduced(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx,
+                                   const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int want_grad,
+                                   int reduction, int average_frames, float norm, float *costs, float *loss,
+                                   float *grads3, void *workspace, size_t workspace_bytes, void *stream) {
+    if ((reduction != 1 && reduction != 2) || !loss || !(norm > 0.0f)) return CTCT_ERR_ARG;
+    return forward_impl(log_probs, dtype, ys, lx, ly, N, T, U1, V, want_grad, costs, grads3, workspace, workspace_bytes,
+                        stream, loss, ReduceSpec{reduction, average_frames ? 1 : 0, norm});
+}
+
+int ctct_b200_loss_backward_reduced(const float *grads3, const float *grad_loss, int reduction, int average_frames,
+                                    float norm, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
+                                    int64_t T, int64_t U1, int64_t V, int dtype, void *dense, void *stream) {
+    if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
+    if ((reduction != 1 && reduction != 2) || !(norm > 0.0f)) return CTCT_ERR_ARG;
+    if (N == 0 || T == 0) return CTCT_OK;
+    if (!grads3 || !grad_loss || !lx || !ly || !dense || (U1 > 1 && !ys)) return CTCT_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(grads3) % 16) return CTCT_ERR_ARG;
+    DenseArgs a;
+    a.GR = reinterpret_cast<const float4 *>(grads3);
+    a.grad_out = grad_loss;
+    a.ys = ys;
+    a.lx = lx;
+    a.ly = ly;
+    a.out = dense;
+    a.T = (int)T;
+    a.U1 = (int)U1;
+    a.V = (int)V;
+    a.vec = 0;
+    a.scalar_grad = 1;
+    a.red = ReduceSpec{reduction, average_frames ? 1 : 0, norm};
+    return dense_backward(a, N, dtype, stream);
 }
 
 int ctct_b200_loss_backward(const float *grads3, const float *grad_out, const int32_t *ys, const int32_t *lx,
@@ -337,18 +410,9 @@ int ctct_b200_loss_backward(const float *grads3, const float *grad_out, const in
     a.U1 = (int)U1;
     a.V = (int)V;
     a.vec = 0;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
-    cudaEvent_t *slot = prof_slot(1);
-    prof_mark(slot, 0, st);
-    int rc = CTCT_ERR_ARG;
-    switch (dtype) {
-    case CTCT_F32: rc = launch_dense_t<float>(a, N, st); break;
-    case CTCT_F16: rc = launch_dense_t<__half>(a, N, st); break;
-    case CTCT_BF16: rc = launch_dense_t<__nv_bfloat16>(a, N, st); break;
-    }
-    prof_mark(slot, 1, st);
-    return rc;
+    a.scalar_grad = 0;
+    a.red = ReduceSpec{0, 0, 1.0f};
+    return dense_backward(a, N, dtype, stream);
 }
 
 int ctct_b200_gather(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx, const int32_t *ly,

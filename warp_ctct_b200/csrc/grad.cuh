@@ -46,6 +46,49 @@ __device__ __forceinline__ float3 occupancies(const float4 *__restrict__ G, cons
     return make_float3(occ0, occ1, occ2);
 }
 
+// How per-utterance costs are folded into one scalar (warp_ctct/__init__.py:138-147):
+// loss = sum_n costs[n] * w[n], w[n] = (average_frames ? 1/lx[n] : 1) * (mean ? 1/norm : 1).
+struct ReduceSpec {
+    int reduction;       // 0 none, 1 sum, 2 mean
+    int average_frames;  // divide each cost by its number of frames first
+    float norm;          // divisor of 'mean' (the global batch size)
+};
+
+__device__ __forceinline__ float utterance_weight(const ReduceSpec &r, int lx_n) {
+    float w = 1.0f;
+    if (r.average_frames) w = 1.0f / static_cast<float>(lx_n);
+    if (r.reduction == 2) w = w / r.norm;
+    return w;
+}
+
+// Deterministic block-wide reduction of the costs (fixed order: strided partial sums, shuffle
+// tree, then the warps in order).  Called by one whole block of 256 threads.
+__device__ __forceinline__ void reduce_costs_block(const float *__restrict__ costs, const int *__restrict__ lx, int N,
+                                                   const ReduceSpec r, float *__restrict__ loss_out) {
+    __shared__ float part[8];
+    float acc = 0.0f;
+    for (int n = threadIdx.x; n < N; n += 256) {
+        float c = costs[n];
+        if (r.average_frames) c = c / static_cast<float>(lx[n]);
+        acc += c;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.0f;
+        for (int w = 0; w < 8; ++w) tot += part[w];
+        if (r.reduction == 2) tot = tot / r.norm;
+        *loss_out = tot;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_reduce_costs(const float *costs, const int *lx, int N, const ReduceSpec r,
+                                                      float *loss_out) {
+    reduce_costs_block(costs, lx, N, r, loss_out);
+}
+
 struct GradArgs {
     const float4 *G;    // [N][T][U1], log2 units
     const float4 *TAB;  // [N][T][2][U1]
@@ -55,6 +98,11 @@ struct GradArgs {
     float *out;         // internal [N][T][U1] float4 {g0,g1,g2,0} or reference [N][T][U1][3]
     int T, U1;
     int ref_layout;
+    // optional fused reduction of the costs (done by block (0,0)); loss_out == nullptr: none
+    const float *costs;
+    float *loss_out;
+    int N;
+    ReduceSpec red;
 };
 
 // One thread per (t,u) of one utterance (blockIdx.y).  Every arc (state at t) -> (state at
@@ -62,6 +110,7 @@ struct GradArgs {
 // exact 0 because one of the two variables is "impossible" there, so the reference's band
 // guards (gather.cu:335-337,355-359) need no restating.
 __global__ void __launch_bounds__(256) k_fill_grad(const GradArgs a) {
+    if (a.loss_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0) reduce_costs_block(a.costs, a.lx, a.N, a.red, a.loss_out);
     const int n = blockIdx.y;
     const int cells = a.T * a.U1;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -120,6 +169,10 @@ struct DenseArgs {
     void *out;              // [N][T][U1][V]
     int T, U1, V;
     int vec;                // 1: V is a multiple of the 16-byte vector width and the base is 16-byte aligned
+    // scalar_grad != 0: grad_out is ONE float (gradient of the reduced loss) and the per-utterance
+    // scale is grad_out[0] * utterance_weight(red, lx[n]); otherwise grad_out holds N floats
+    int scalar_grad;
+    ReduceSpec red;
 };
 
 // What one row of the dense gradient holds besides zeros: column 0 and up to two label columns.
@@ -132,7 +185,7 @@ struct RowPatch {
 // Columns that coincide add up in slot order, each product rounded to OutT first -- what a
 // cast followed by scatter_add onto zeros produces.
 template <typename OutT>
-__device__ __forceinline__ RowPatch<OutT> make_patch(const float4 g, float go, const int *__restrict__ y, int u, int Un,
+__device__ __forceinline__ RowPatch<OutT> make_patch(const float4 g, float go, int y_prev, int y_next, int u, int Un,
                                                      int V) {
     using O = OutOps<OutT>;
     RowPatch<OutT> p;
@@ -143,11 +196,11 @@ __device__ __forceinline__ RowPatch<OutT> make_patch(const float4 g, float go, c
     p.i1 = -1;
     p.i2 = -1;
     if (u >= 1) {
-        p.i1 = min(max(y[u - 1], 0), V - 1);
+        p.i1 = min(max(y_prev, 0), V - 1);
         p.c1 = O::add(zero, O::cvt(go * g.y));
     }
     if (u < Un) {
-        p.i2 = min(max(y[u], 0), V - 1);
+        p.i2 = min(max(y_next, 0), V - 1);
         p.c2 = O::add(zero, O::cvt(go * g.z));
     }
     if (p.i1 == 0) {
@@ -191,14 +244,26 @@ __global__ void __launch_bounds__(256) k_dense_grad(const DenseArgs a) {
     const int Tn = min(a.lx[n], a.T);
     const int Un = (t < Tn) ? min(a.ly[n], U) : -1;  // rows u <= Un carry values
     const int *y = a.ys + static_cast<int64_t>(n) * U;
-    const float go = (Un >= 0) ? a.grad_out[n] : 0.0f;
+    float go = 0.0f;
+    if (Un >= 0) go = a.scalar_grad ? a.grad_out[0] * utterance_weight(a.red, a.lx[n]) : a.grad_out[n];
     const float4 *gr = a.GR + slab * a.U1;
 
+    // record and labels of a row are fetched one row ahead of the stores that need them
     float4 g_next = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (warp <= Un) g_next = gr[warp];
+    int yp_next = 0, yn_next = 0;
+    if (warp <= Un) {
+        g_next = gr[warp];
+        if (warp >= 1) yp_next = y[warp - 1];
+        if (warp < Un) yn_next = y[warp];
+    }
     for (int u = warp; u < a.U1; u += 8) {
         const float4 g = g_next;
-        if (u + 8 <= Un) g_next = gr[u + 8];
+        const int y_prev = yp_next, y_nxt = yn_next;
+        if (u + 8 <= Un) {
+            g_next = gr[u + 8];
+            yp_next = y[u + 7];
+            if (u + 8 < Un) yn_next = y[u + 8];
+        }
         OutT *row = base + static_cast<int64_t>(u) * V;
         if (u > Un) {  // padding row
             if (a.vec) {
@@ -211,7 +276,7 @@ __global__ void __launch_bounds__(256) k_dense_grad(const DenseArgs a) {
             }
             continue;
         }
-        const RowPatch<OutT> p = make_patch<OutT>(g, go, y, u, Un, V);
+        const RowPatch<OutT> p = make_patch<OutT>(g, go, y_prev, y_nxt, u, Un, V);
         if (a.vec) {
             uint4 *dv = reinterpret_cast<uint4 *>(row);
             const int j1 = p.i1 >= 0 ? p.i1 / E : -1, j2 = p.i2 >= 0 ? p.i2 / E : -1;

@@ -28,6 +28,8 @@
 // Read per context as one float4 {label value, offset, blank value, offset}.
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace ctct {
@@ -152,7 +154,6 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
     }
     float adj = 0.0f;        // neighbour warp's offset minus ours
     bool untouched = true;   // no state of this warp reachable yet (as of the last renormalisation)
-    bool refresh = false;    // offsets changed in the previous frame: re-read the neighbour's
 
     const int nchunks = (Tn + F - 1) / F;
     auto chunk_range = [&](int c, int &lo, int &hi) {
@@ -172,31 +173,117 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
         for (int v = tid; v < nvec; v += NT) cp_async16(dst + v, src + v);
         cp_async_commit();
     };
-    // reload the halo lanes from what the neighbouring warp published in buffer `par`
-    auto load_halo = [&](int par) {
-        if (!MULTI) return;
-        if (refresh) {
-            const int offp = xo[e_in];
-            if (untouched) off = offp;  // adopt the neighbour's scale until something arrives
-            adj = static_cast<float>(offp - off);
-        }
-        const float *in = xs + (par * (W + 1) + e_in) * 2;
-        if (DIR == 0) {
+    // exchange pointers of this thread for the two buffers (parity of the frame number)
+    const bool loader = MULTI && ((C == 1) ? halo : (DIR == 0 ? lane == 0 : lane == 31));
+    const bool publisher = MULTI && ((DIR == 0) ? (C == 1 ? lane >= 30 : lane == 31) : (C == 1 ? lane < 2 : lane == 0));
+    const int lane_in = (C == 1) ? (DIR == 0 ? lane : lane - 30) : 0;
+    const int lane_out = (C == 1) ? (DIR == 0 ? lane - 30 : lane) : 0;
+    const float *in_p[2] = {xs + (0 * (W + 1) + e_in) * 2 + (loader ? lane_in : 0),
+                            xs + (1 * (W + 1) + e_in) * 2 + (loader ? lane_in : 0)};
+    float *out_p[2] = {xs + (0 * (W + 1) + e_pub) * 2 + (publisher ? lane_out : 0),
+                       xs + (1 * (W + 1) + e_pub) * 2 + (publisher ? lane_out : 0)};
+    const bool off_publisher = MULTI && lane == (DIR == 0 ? 31 : 0);
+
+    const float *row = nullptr;
+    float2 *tr = nullptr;
+
+    // One frame.  PAR = parity of the frame number: buffer PAR holds what the neighbours published
+    // at the end of the previous frame, buffer PAR^1 receives this frame's; even frames renormalise.
+    auto frame_step = [&](auto PAR) {
+        constexpr int par = decltype(PAR)::value;
+        constexpr bool renorm = (par % RENORM) == 0;
+        if (MULTI) {
+            if (par == 1) {  // offsets changed in the previous (even) frame: re-read the neighbour's
+                const int offp = xo[e_in];
+                if (untouched) off = offp;  // adopt the neighbour's scale until something arrives
+                adj = static_cast<float>(offp - off);
+            }
             if (C == 1) {
-                if (lane < 2) x[0] = in[lane] + adj;
-            } else if (lane == 0) {
-                x[C >= 2 ? C - 2 : 0] = in[0] + adj;
-                x[C - 1] = in[1] + adj;
+                if (loader) x[0] = in_p[par][0] + adj;
+            } else if (loader) {
+                x[DIR == 0 ? (C >= 2 ? C - 2 : 0) : 0] = in_p[par][0] + adj;
+                x[DIR == 0 ? C - 1 : (C >= 2 ? 1 : 0)] = in_p[par][1] + adj;
+            }
+        }
+        if (renorm) {  // subtract the rounded warp maximum, keep it in the integer offset
+            int ki = __float2int_rn(x[0]);
+#pragma unroll
+            for (int cc = 1; cc < C; ++cc) ki = max(ki, __float2int_rn(x[cc]));
+            ki = __reduce_max_sync(FULL, ki);
+            untouched = ki < -(1 << 30);
+            if (!untouched) {
+                const float k = static_cast<float>(ki);
+#pragma unroll
+                for (int cc = 0; cc < C; ++cc) x[cc] -= k;
+                off += ki;
+            }
+        }
+        if (store) {
+#pragma unroll
+            for (int cc = 0; cc < C; ++cc)
+                if (real[cc]) tr[cc] = make_float2(x[cc], __int_as_float(off));
+        }
+
+        // neighbours: slot j-1, j-2 (alpha) or j+1, j+2 (beta)
+        float n1, n2;  // for the first (alpha) / last (beta) slot of this thread
+        if (DIR == 0) {
+            n1 = __shfl_up_sync(FULL, x[C - 1], 1);
+            n2 = (C >= 2) ? __shfl_up_sync(FULL, x[C >= 2 ? C - 2 : 0], 1) : __shfl_up_sync(FULL, x[0], 2);
+            if (!MULTI) {
+                if (lane == 0) n1 = NEG;
+                if (lane == 0 || (C == 1 && lane == 1)) n2 = NEG;
             }
         } else {
-            if (C == 1) {
-                if (lane >= 30) x[0] = in[lane - 30] + adj;
-            } else if (lane == 31) {
-                x[0] = in[0] + adj;
-                x[C >= 2 ? 1 : 0] = in[1] + adj;
+            n1 = __shfl_down_sync(FULL, x[0], 1);
+            n2 = (C >= 2) ? __shfl_down_sync(FULL, x[C >= 2 ? 1 : 0], 1) : __shfl_down_sync(FULL, x[0], 2);
+            if (!MULTI) {
+                if (lane == 31) n1 = NEG;
+                if (lane == 31 || (C == 1 && lane == 30)) n2 = NEG;
             }
         }
+
+        // one step of the recursion for every slot of this thread
+        float nx[C];
+#pragma unroll
+        for (int cc = 0; cc < C; ++cc) {
+            float v1, v2;
+            if (DIR == 0) {
+                v1 = (cc >= 1) ? x[cc >= 1 ? cc - 1 : 0] : n1;
+                v2 = (cc >= 2) ? x[cc >= 2 ? cc - 2 : 0] : ((cc == 1) ? n1 : n2);
+            } else {
+                v1 = (cc + 1 < C) ? x[cc + 1 < C ? cc + 1 : 0] : n1;
+                v2 = (cc + 2 < C) ? x[cc + 2 < C ? cc + 2 : 0] : ((cc + 2 == C) ? n1 : n2);
+            }
+            const float ps = row[ofs_s[cc]];
+            const float pa = row[ofs_a[cc]] + mask_a[cc];
+            float pk = pa;
+            if (DIR == 1) pk = row[(ofs_s[cc] & ~3) + 2];  // next-label emission of the same context
+            const float t3 = skip[cc] ? v2 + pk : NEG;
+            nx[cc] = lse3(x[cc] + ps, v1 + pa, t3);
+        }
+#pragma unroll
+        for (int cc = 0; cc < C; ++cc) x[cc] = nx[cc];
+
+        // publish this warp's boundary slots into buffer par^1 (and its offset after a
+        // renormalisation); the barrier orders them before the neighbour's reload
+        if (MULTI) {
+            if (publisher) {
+                if (C == 1) {
+                    out_p[par ^ 1][0] = x[0];
+                } else {
+                    out_p[par ^ 1][0] = x[DIR == 0 ? (C >= 2 ? C - 2 : 0) : 0];
+                    out_p[par ^ 1][1] = x[DIR == 0 ? C - 1 : (C >= 2 ? 1 : 0)];
+                }
+            }
+            if (renorm && off_publisher) xo[e_pub] = off;
+            __syncthreads();
+        }
+        constexpr int tstep = (DIR == 0) ? 1 : -1;
+        row += tstep * 4 * U1;
+        tr += tstep * 2 * S2;
     };
+    using Even = std::integral_constant<int, 0>;
+    using Odd = std::integral_constant<int, 1>;
 
     int frame = 0;
     if (nchunks > 0) issue(0, buf0);
@@ -215,101 +302,23 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
         int lo, hi;
         chunk_range(c, lo, hi);
         const int nf = hi - lo;
-        constexpr int tstep = (DIR == 0) ? 1 : -1;
-        int t = (DIR == 0) ? lo : hi - 1;
-        const float *row = reinterpret_cast<const float *>(cur + static_cast<int64_t>(t - lo) * U1);
-        float2 *tr = a.TAB + ((rowbase + t) * 2 + DIR) * S2 + j0;
-#pragma unroll 2
-        for (int f = 0; f < nf; ++f, ++frame, t += tstep, row += tstep * 4 * U1, tr += tstep * 2 * S2) {
-            const int par = frame & 1;
-            load_halo(par);  // values published at the end of the previous frame (buffer par)
-            // ---- renormalise (warp-uniform), every RENORM frames: subtract the rounded warp maximum
-            const bool renorm = (frame % RENORM) == 0;
-            refresh = false;
-            if (renorm) {
-                int ki = __float2int_rn(x[0]);
-#pragma unroll
-                for (int cc = 1; cc < C; ++cc) ki = max(ki, __float2int_rn(x[cc]));
-                ki = __reduce_max_sync(FULL, ki);
-                untouched = ki < -(1 << 30);
-                if (!untouched) {
-                    const float k = static_cast<float>(ki);
-#pragma unroll
-                    for (int cc = 0; cc < C; ++cc) x[cc] -= k;
-                    off += ki;
-                }
-                refresh = true;
-            }
-            if (store) {
-#pragma unroll
-                for (int cc = 0; cc < C; ++cc)
-                    if (real[cc]) tr[cc] = make_float2(x[cc], __int_as_float(off));
-            }
-
-            // ---- neighbours: slot j-1, j-2 (alpha) or j+1, j+2 (beta)
-            float n1, n2;  // for the first (alpha) / last (beta) slot of this thread
-            if (DIR == 0) {
-                n1 = __shfl_up_sync(FULL, x[C - 1], 1);
-                n2 = (C >= 2) ? __shfl_up_sync(FULL, x[C >= 2 ? C - 2 : 0], 1) : __shfl_up_sync(FULL, x[0], 2);
-                if (!MULTI) {
-                    if (lane == 0) n1 = NEG;
-                    if (lane == 0 || (C == 1 && lane == 1)) n2 = NEG;
-                }
-            } else {
-                n1 = __shfl_down_sync(FULL, x[0], 1);
-                n2 = (C >= 2) ? __shfl_down_sync(FULL, x[C >= 2 ? 1 : 0], 1) : __shfl_down_sync(FULL, x[0], 2);
-                if (!MULTI) {
-                    if (lane == 31) n1 = NEG;
-                    if (lane == 31 || (C == 1 && lane == 30)) n2 = NEG;
-                }
-            }
-
-            // ---- one step of the recursion for every slot of this thread
-            float nx[C];
-#pragma unroll
-            for (int cc = 0; cc < C; ++cc) {
-                float v1, v2;
-                if (DIR == 0) {
-                    v1 = (cc >= 1) ? x[cc >= 1 ? cc - 1 : 0] : n1;
-                    v2 = (cc >= 2) ? x[cc >= 2 ? cc - 2 : 0] : ((cc == 1) ? n1 : n2);
-                } else {
-                    v1 = (cc + 1 < C) ? x[cc + 1 < C ? cc + 1 : 0] : n1;
-                    v2 = (cc + 2 < C) ? x[cc + 2 < C ? cc + 2 : 0] : ((cc + 2 == C) ? n1 : n2);
-                }
-                const float ps = row[ofs_s[cc]];
-                const float pa = row[ofs_a[cc]] + mask_a[cc];
-                float pk = pa;
-                if (DIR == 1) pk = row[(ofs_s[cc] & ~3) + 2];  // next-label emission of the same context
-                const float t3 = skip[cc] ? v2 + pk : NEG;
-                nx[cc] = lse3(x[cc] + ps, v1 + pa, t3);
-            }
-#pragma unroll
-            for (int cc = 0; cc < C; ++cc) x[cc] = nx[cc];
-
-            // ---- publish this warp's boundary slots (buffer par^1) and, after a renormalisation,
-            // its offset; the barrier orders them before the neighbour's reload
-            if (MULTI) {
-                float *out = xs + ((par ^ 1) * (W + 1) + e_pub) * 2;
-                if (DIR == 0) {
-                    if (C == 1) {
-                        if (lane >= 30) out[lane - 30] = x[0];
-                    } else if (lane == 31) {
-                        out[0] = x[C >= 2 ? C - 2 : 0];
-                        out[1] = x[C - 1];
-                    }
-                    if (renorm && lane == 31) xo[e_pub] = off;
-                } else {
-                    if (C == 1) {
-                        if (lane < 2) out[lane] = x[0];
-                    } else if (lane == 0) {
-                        out[0] = x[0];
-                        out[1] = x[C >= 2 ? 1 : 0];
-                    }
-                    if (renorm && lane == 0) xo[e_pub] = off;
-                }
-                __syncthreads();
+        const int t0 = (DIR == 0) ? lo : hi - 1;
+        row = reinterpret_cast<const float *>(cur + static_cast<int64_t>(t0 - lo) * U1);
+        tr = a.TAB + ((rowbase + t0) * 2 + DIR) * S2 + j0;
+        int f = 0;
+        if ((frame & 1) == 0) {
+            for (; f + 1 < nf; f += 2) {
+                frame_step(Even{});
+                frame_step(Odd{});
             }
         }
+        for (; f < nf; ++f) {
+            if ((frame + f) & 1)
+                frame_step(Odd{});
+            else
+                frame_step(Even{});
+        }
+        frame += nf;
         if (MULTI)
             __syncthreads();
         else

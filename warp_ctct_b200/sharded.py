@@ -12,7 +12,7 @@ from typing import List, Optional, Sequence
 import torch
 import torch.distributed as dist
 
-from . import FusedCTCTLoss, _as_int, _require_cuda
+from . import FusedCTCTLoss, FusedCTCTLossReduced, _as_int, _require_cuda
 
 
 def plan_shards(frames_lengths: Sequence[int], labels_lengths: Sequence[int], world_size: int) -> List[List[int]]:
@@ -92,6 +92,13 @@ def sharded_ctct_loss(log_probs: torch.Tensor, labels: torch.Tensor, frames_leng
         log_probs = log_probs.float()
     if not log_probs.is_contiguous():
         log_probs = log_probs.contiguous()
+    if reduction in ("mean", "sum") and log_probs.size(0) > 0:
+        # this rank's share of the global loss straight out of the kernels (for 'mean' already
+        # divided by the global batch); the all-reduce of that one float completes it
+        part = FusedCTCTLossReduced.apply(log_probs, _as_int(labels), _as_int(frames_lengths),
+                                          _as_int(labels_lengths), enable_grad, reduction == "mean",
+                                          bool(average_frames), float(global_batch))
+        return part if world == 1 else all_reduce_sum(part, group)
     costs = FusedCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
                                 enable_grad)
     return reduce_costs(costs, frames_lengths, global_batch, reduction, average_frames, group)
