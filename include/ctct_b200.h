@@ -127,6 +127,22 @@ int ctct_b200_loss_backward_reduced(const float *grads3, const float *grad_loss,
                                     void *dense, void *stream);
 
 /*
+ * Two-step form of the dense gradient, for callers that can clear the buffer early (before the
+ * gradient scale exists, e.g. on a second stream while the latency-bound lattice runs):
+ *   ctct_b200_zero_fill            streams zeros over `bytes` bytes (16-byte aligned buffer);
+ *   ctct_b200_loss_backward_patch  writes the <= 3 non-zero columns of every live row into a
+ *                                  buffer that is already zero.
+ * Together they produce exactly what ctct_b200_loss_backward (scalar_grad == 0, `grad` = N floats)
+ * or ctct_b200_loss_backward_reduced (scalar_grad != 0, `grad` = one float) produce in one pass.
+ * Same reference counterpart: warp_ctct/__init__.py:31-33 and the autograd backward of :131.
+ */
+int ctct_b200_zero_fill(void *buffer, size_t bytes, void *stream);
+int ctct_b200_loss_backward_patch(const float *grads3, const float *grad, int scalar_grad, int reduction,
+                                  int average_frames, float norm, const int32_t *ys, const int32_t *lx,
+                                  const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int dtype,
+                                  void *dense, void *stream);
+
+/*
  * The gather alone, in the reference's layout: gathered[n,t,u,0..2] =
  * log_probs[n,t,u,{0, ys[n,u-1], ys[n,u]}] converted to float32 (slots without a
  * label read column 0).  Replaces collect_units (ref_ctct.py:223-230) /
@@ -222,8 +238,8 @@ int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const 
  * Events are created once by _enable (room for max_calls calls, shared by all host threads) and
  * destroyed by _disable; nothing is recorded when profiling is off.
  *   ctct_b200_profile_read: waits for the recorded events, writes for call i
- *     kind[i] (0 forward, 1 backward) and ms[4*i .. 4*i+2] = {gather, lattice, fill_grad}
- *     or {dense gradient, 0, 0}; returns the number of calls recorded (<= capacity) or a
+ *     kind[i] (0 forward, 1 backward, 2 zero fill) and ms[4*i .. 4*i+2] = {gather, lattice,
+ *     fill_grad} or {dense gradient / patch / zero fill, 0, 0}; returns the number of calls recorded (<= capacity) or a
  *     negative error code, and rewinds the recorder.
  */
 int ctct_b200_profile_enable(int max_calls);

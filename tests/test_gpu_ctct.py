@@ -252,6 +252,40 @@ def test_dense_gradient_fp32(W, shape, seed, kw):
         np.testing.assert_allclose(-got[n, :lx[n]].sum((1, 2)), go[n], rtol=2e-5)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_precleared_and_one_pass_gradients_are_identical(W, dtype, monkeypatch):
+    """The backward pass either writes the whole gradient in one pass or patches a buffer that the
+    forward pass cleared on a second stream; both must give the same bits, also for a second
+    backward through a retained graph (which has no pre-cleared buffer left)."""
+    N, T, U1, V = 3, 30, 9, 70   # V*2 bytes not a multiple of 16 for fp16: scalar store path too
+    lp, ys, lx, ly = make_case(N, T, U1, V, 1.5, 91, lx_range=(15, 30), ly_range=(2, 8), repeat_prob=0.3)
+    ys[1, :3] = 0                # labels that collide with the blank column
+    go = torch.tensor([0.5, 2.0, 1.25], device=DEV)
+    ys_t, lx_t, ly_t = _dev(ys, lx, ly)
+    grads = {}
+    for mode in ("one_pass", "precleared"):
+        monkeypatch.setattr(W, "PREZERO", mode == "precleared")
+        monkeypatch.setattr(W, "PREZERO_MIN_BYTES", 0)
+        for red in ("none", "mean"):
+            x = torch.from_numpy(lp).to(DEV).to(dtype).requires_grad_(True)
+            loss = W.ctct_loss(x, ys_t, lx_t, ly_t, reduction=red, average_frames=True)
+            if red == "none":
+                loss.backward(go, retain_graph=True)
+                first = x.grad.clone()
+                x.grad = None
+                loss.backward(go)          # second pass: always the one-pass kernel
+                assert torch.equal(first, x.grad)
+            else:
+                loss.backward()
+            grads[(mode, red)] = x.grad.clone()
+    for red in ("none", "mean"):
+        assert torch.equal(grads[("one_pass", red)], grads[("precleared", red)]), red
+    _, dense = oracle.ctct_loss(torch.from_numpy(lp).to(dtype).float().numpy(), ys, lx, ly,
+                                (go.cpu().numpy() / lx).astype(np.float32))
+    tol = 1e-4 if dtype == torch.float32 else 2e-3
+    assert np.abs(grads[("precleared", "none")].float().cpu().numpy() - dense).max() < tol
+
+
 @pytest.mark.parametrize("dtype,ulp", [(torch.float16, 2.0 ** -11), (torch.bfloat16, 2.0 ** -8)])
 def test_dense_gradient_16bit(W, dtype, ulp):
     N, T, U1, V = 3, 40, 17, 264

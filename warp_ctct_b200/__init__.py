@@ -9,6 +9,7 @@ blank = 0
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -32,6 +33,37 @@ def _as_int(t: T) -> T:
     return t.to(torch.int32).contiguous()
 
 
+# The dense gradient is zero except for <= 3 columns per row, and clearing it needs nothing the
+# forward pass computes.  With PREZERO on, the forward pass allocates the gradient and clears it on
+# a second stream while the (latency-bound) lattice runs; the backward pass then only patches the
+# non-zero columns.  Off (or for small tensors, or on a second backward through the same graph)
+# the backward pass writes the whole tensor in one pass.  Set CTCT_B200_PREZERO=0 to turn it off.
+PREZERO = os.environ.get("CTCT_B200_PREZERO", "1") != "0"
+PREZERO_MIN_BYTES = 8 << 20
+_side_streams = {}
+
+
+def _start_prezero(dev, shape, dtype):
+    """Allocate the dense gradient and start clearing it on the side stream of ``dev``.
+    Returns (tensor, event recorded after the clear) or None when pre-clearing is not worthwhile."""
+    nbytes = torch.empty((), dtype=dtype).element_size()
+    for d in shape:
+        nbytes *= d
+    if not PREZERO or nbytes < PREZERO_MIN_BYTES or torch.cuda.is_current_stream_capturing():
+        return None
+    cur = torch.cuda.current_stream(dev)
+    side = _side_streams.get(dev.index)
+    if side is None:
+        side = _side_streams[dev.index] = torch.cuda.Stream(dev)
+    dense = torch.empty(shape, dtype=dtype, device=dev)
+    side.wait_stream(cur)  # whatever used this memory before was enqueued on the current stream
+    _lib.check(_lib.lib().ctct_b200_zero_fill(dense.data_ptr(), nbytes, side.cuda_stream), "ctct_b200_zero_fill")
+    done = torch.cuda.Event()
+    done.record(side)
+    dense.record_stream(side)
+    return dense, done
+
+
 class FusedCTCTLoss(torch.autograd.Function):
     """costs = CTC-T loss of the FULL joint tensor (N,T,U+1,V); gather, lattice and the
     occupancy gradient are fused behind one C-ABI call, the dense gradient behind another.
@@ -45,6 +77,7 @@ class FusedCTCTLoss(torch.autograd.Function):
         lib = _lib.lib()
         costs = torch.empty((N,), dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
+            ctx.prezero = _start_prezero(dev, (N, Tm, U1, V), log_probs.dtype) if requires_grad else None
             ws = _lib.workspace(N, Tm, U1, requires_grad, dev)
             grads3 = None
             if requires_grad:
@@ -65,11 +98,19 @@ class FusedCTCTLoss(torch.autograd.Function):
         N, Tm, U1, V, dtype = ctx.meta
         dev = grads3.device
         go = grad_outputs.to(torch.float32).contiguous()
-        dense = torch.empty((N, Tm, U1, V), dtype=dtype, device=dev)
+        pre, ctx.prezero = ctx.prezero, None
         with torch.cuda.device(dev):
-            rc = _lib.lib().ctct_b200_loss_backward(
-                _lib.ptr(grads3), _lib.ptr(go), _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
-                N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
+            if pre is not None:
+                dense, cleared = pre
+                torch.cuda.current_stream(dev).wait_event(cleared)
+                rc = _lib.lib().ctct_b200_loss_backward_patch(
+                    _lib.ptr(grads3), _lib.ptr(go), 0, 0, 0, 1.0, _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
+                    N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
+            else:
+                dense = torch.empty((N, Tm, U1, V), dtype=dtype, device=dev)
+                rc = _lib.lib().ctct_b200_loss_backward(
+                    _lib.ptr(grads3), _lib.ptr(go), _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
+                    N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
         _lib.check(rc, "ctct_b200_loss_backward")
         return dense, None, None, None, None
 
@@ -88,6 +129,7 @@ class FusedCTCTLossReduced(torch.autograd.Function):
         red = 2 if mean else 1
         out = torch.empty((N + 1,), dtype=torch.float32, device=dev)  # [loss, costs...]
         with torch.cuda.device(dev):
+            ctx.prezero = _start_prezero(dev, (N, Tm, U1, V), log_probs.dtype) if requires_grad else None
             ws = _lib.workspace(N, Tm, U1, requires_grad, dev)
             grads3 = None
             if requires_grad:
@@ -108,11 +150,19 @@ class FusedCTCTLossReduced(torch.autograd.Function):
         N, Tm, U1, V, dtype, red, avg, norm = ctx.meta
         dev = grads3.device
         go = grad_loss.to(torch.float32).contiguous()
-        dense = torch.empty((N, Tm, U1, V), dtype=dtype, device=dev)
+        pre, ctx.prezero = ctx.prezero, None
         with torch.cuda.device(dev):
-            rc = _lib.lib().ctct_b200_loss_backward_reduced(
-                _lib.ptr(grads3), _lib.ptr(go), red, int(avg), norm, _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
-                N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
+            if pre is not None:
+                dense, cleared = pre
+                torch.cuda.current_stream(dev).wait_event(cleared)
+                rc = _lib.lib().ctct_b200_loss_backward_patch(
+                    _lib.ptr(grads3), _lib.ptr(go), 1, red, int(avg), norm, _lib.ptr(labels), _lib.ptr(lx),
+                    _lib.ptr(ly), N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
+            else:
+                dense = torch.empty((N, Tm, U1, V), dtype=dtype, device=dev)
+                rc = _lib.lib().ctct_b200_loss_backward_reduced(
+                    _lib.ptr(grads3), _lib.ptr(go), red, int(avg), norm, _lib.ptr(labels), _lib.ptr(lx),
+                    _lib.ptr(ly), N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
         _lib.check(rc, "ctct_b200_loss_backward_reduced")
         return dense, None, None, None, None, None, None, None
 

@@ -51,6 +51,25 @@ __device__ __forceinline__ float load_as_float(const __nv_bfloat16 *p) {
     return __bfloat162float(__ushort_as_bfloat16(__ldg(reinterpret_cast<const unsigned short *>(p))));
 }
 
+// Isolated element reads (one element out of a 2-4 KB vocabulary row): non-coherent, no L1
+// allocation, and the smallest L2 fetch granule, so that a 4-byte read does not pull a 128-byte
+// line out of HBM.
+__device__ __forceinline__ float load_sparse(const float *p) {
+    float v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::64B.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float load_sparse(const __half *p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::64B.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return __half2float(__ushort_as_half(v));
+}
+__device__ __forceinline__ float load_sparse(const __nv_bfloat16 *p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::64B.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return __bfloat162float(__ushort_as_bfloat16(v));
+}
+
 __host__ __device__ __forceinline__ int64_t pad4(int64_t x) { return (x + 3) & ~int64_t(3); }
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {

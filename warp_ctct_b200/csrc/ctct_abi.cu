@@ -274,16 +274,34 @@ int launch_logmm_bwd(const LogmmBwdArgs &a, int64_t B, cudaStream_t st) {
     return CTCT_ERR_UNSUPPORTED;
 }
 
+template <typename OutT>
+int launch_patch_t(const DenseArgs &a, int64_t N, cudaStream_t st) {
+    const int64_t rows = N * a.T * a.U1;
+    if (rows == 0) return CTCT_OK;
+    const int64_t want = (rows + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+    k_dense_patch<OutT><<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(a, rows);
+    return check_launch("dense_patch");
+}
+
 int dense_backward(DenseArgs a, int64_t N, int dtype, void *stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
     cudaEvent_t *slot = prof_slot(1);
     prof_mark(slot, 0, st);
     int rc = CTCT_ERR_ARG;
-    switch (dtype) {
-    case CTCT_F32: rc = launch_dense_t<float>(a, N, st); break;
-    case CTCT_F16: rc = launch_dense_t<__half>(a, N, st); break;
-    case CTCT_BF16: rc = launch_dense_t<__nv_bfloat16>(a, N, st); break;
+    if (a.vec == 2) {  // the buffer was cleared beforehand: only patch
+        switch (dtype) {
+        case CTCT_F32: rc = launch_patch_t<float>(a, N, st); break;
+        case CTCT_F16: rc = launch_patch_t<__half>(a, N, st); break;
+        case CTCT_BF16: rc = launch_patch_t<__nv_bfloat16>(a, N, st); break;
+        }
+    } else {
+        switch (dtype) {
+        case CTCT_F32: rc = launch_dense_t<float>(a, N, st); break;
+        case CTCT_F16: rc = launch_dense_t<__half>(a, N, st); break;
+        case CTCT_BF16: rc = launch_dense_t<__nv_bfloat16>(a, N, st); break;
+        }
     }
     prof_mark(slot, 1, st);
     return rc;
@@ -412,6 +430,48 @@ int ctct_b200_loss_backward(const float *grads3, const float *grad_out, const in
     a.vec = 0;
     a.scalar_grad = 0;
     a.red = ReduceSpec{0, 0, 1.0f};
+    return dense_backward(a, N, dtype, stream);
+}
+
+int ctct_b200_zero_fill(void *buffer, size_t bytes, void *stream) {
+    if (bytes == 0) return CTCT_OK;
+    if (!buffer || reinterpret_cast<uintptr_t>(buffer) % 16) return CTCT_ERR_ARG;
+    const size_t nvec = bytes / 16;
+    const int tail = static_cast<int>(bytes % 16);
+    const size_t blocks = (nvec + 1023) / 1024;
+    if (blocks > 0x7fffffff) return CTCT_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaEvent_t *slot = prof_slot(2);
+    prof_mark(slot, 0, st);
+    k_zero_fill<<<static_cast<unsigned>(blocks ? blocks : 1), 256, 0, st>>>(
+        static_cast<uint4 *>(buffer), nvec, static_cast<unsigned char *>(buffer) + nvec * 16, tail);
+    const int rc = check_launch("zero_fill");
+    prof_mark(slot, 1, st);
+    return rc;
+}
+
+int ctct_b200_loss_backward_patch(const float *grads3, const float *grad, int scalar_grad, int reduction,
+                                  int average_frames, float norm, const int32_t *ys, const int32_t *lx,
+                                  const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int dtype,
+                                  void *dense, void *stream) {
+    if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
+    if (scalar_grad && ((reduction != 1 && reduction != 2) || !(norm > 0.0f))) return CTCT_ERR_ARG;
+    if (N == 0 || T == 0) return CTCT_OK;
+    if (!grads3 || !grad || !lx || !ly || !dense || (U1 > 1 && !ys)) return CTCT_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(grads3) % 16) return CTCT_ERR_ARG;
+    DenseArgs a;
+    a.GR = reinterpret_cast<const float4 *>(grads3);
+    a.grad_out = grad;
+    a.ys = ys;
+    a.lx = lx;
+    a.ly = ly;
+    a.out = dense;
+    a.T = (int)T;
+    a.U1 = (int)U1;
+    a.V = (int)V;
+    a.vec = 2;
+    a.scalar_grad = scalar_grad ? 1 : 0;
+    a.red = ReduceSpec{scalar_grad ? reduction : 0, average_frames ? 1 : 0, scalar_grad ? norm : 1.0f};
     return dense_backward(a, N, dtype, stream);
 }
 
@@ -643,7 +703,7 @@ int ctct_b200_profile_read(float *ms, int *kind, int capacity) {
     const int n = g_prof.used < capacity ? g_prof.used : capacity;
     for (int i = 0; i < n; ++i) {
         cudaEvent_t *e = g_prof.ev + 4 * i;
-        const int pairs = g_prof.kind[i] == 0 ? 3 : 1;
+        const int pairs = g_prof.kind[i] == 0 ? 3 : 1;  // forward: three intervals; others: one
         if (cudaEventSynchronize(e[pairs]) != cudaSuccess) return check_launch("profile sync");
         kind[i] = g_prof.kind[i];
         for (int k = 0; k < 3; ++k) {

@@ -57,7 +57,7 @@ k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__r
                     if (k == 2 && u < U && (!valid_only || u < ly[n])) idx = ys[static_cast<int64_t>(n) * U + u];
                     idx = min(max(idx, 0), V - 1);
                     const int64_t row = static_cast<int64_t>(nt) * U1 + u;
-                    const float x = load_as_float(lp + row * V + idx);
+                    const float x = load_sparse(lp + row * V + idx);
                     val[j] = INTERNAL ? to_log2(x) : x;
                 }
             }

@@ -241,25 +241,24 @@ __global__ void __launch_bounds__(256) k_dense_grad(const DenseArgs a) {
     const int U = a.U1 - 1, V = a.V;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     OutT *base = static_cast<OutT *>(a.out) + slab * static_cast<int64_t>(a.U1) * V;
-    const int Tn = min(a.lx[n], a.T);
-    const int Un = (t < Tn) ? min(a.ly[n], U) : -1;  // rows u <= Un carry values
     const int *y = a.ys + static_cast<int64_t>(n) * U;
-    float go = 0.0f;
-    if (Un >= 0) go = a.scalar_grad ? a.grad_out[0] * utterance_weight(a.red, a.lx[n]) : a.grad_out[n];
     const float4 *gr = a.GR + slab * a.U1;
+    // Everything the first row needs is requested at once, whether or not it turns out to be
+    // needed (all addresses are inside the buffers), so that the CTA pays one memory latency
+    // before its first store, not a chain of them.
+    const int lx_n = a.lx[n], ly_n = a.ly[n];
+    const float go_raw = a.scalar_grad ? a.grad_out[0] : a.grad_out[n];
+    float4 g_next = gr[min(warp, U)];
+    int yp_next = (U > 0) ? y[min(max(warp - 1, 0), U - 1)] : 0;
+    int yn_next = (U > 0) ? y[min(warp, U - 1)] : 0;
+    const int Tn = min(lx_n, a.T);
+    const int Un = (t < Tn) ? min(ly_n, U) : -1;  // rows u <= Un carry values
+    const float go = a.scalar_grad ? go_raw * utterance_weight(a.red, lx_n) : go_raw;
 
-    // record and labels of a row are fetched one row ahead of the stores that need them
-    float4 g_next = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    int yp_next = 0, yn_next = 0;
-    if (warp <= Un) {
-        g_next = gr[warp];
-        if (warp >= 1) yp_next = y[warp - 1];
-        if (warp < Un) yn_next = y[warp];
-    }
     for (int u = warp; u < a.U1; u += 8) {
         const float4 g = g_next;
         const int y_prev = yp_next, y_nxt = yn_next;
-        if (u + 8 <= Un) {
+        if (u + 8 <= Un) {  // one row ahead
             g_next = gr[u + 8];
             yp_next = y[u + 7];
             if (u + 8 < Un) yn_next = y[u + 8];
@@ -310,6 +309,50 @@ __global__ void __launch_bounds__(256) k_dense_grad(const DenseArgs a) {
                 row[c] = x;
             }
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Two-step alternative to k_dense_grad, for callers that can start clearing the gradient buffer
+// before the gradient scale is known (e.g. on a second stream while the lattice runs):
+// k_zero_fill streams zeros, k_dense_patch later writes the <= 3 non-zero columns of every live row.
+
+// Each block clears one contiguous chunk of 1024 16-byte vectors (4 per thread, strided by the
+// block): many short blocks reach the HBM write peak, a persistent grid does not.
+__global__ void __launch_bounds__(256) k_zero_fill(uint4 *__restrict__ out, size_t nvec, unsigned char *__restrict__ tail,
+                                                   int tail_bytes) {
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    const size_t base = static_cast<size_t>(blockIdx.x) * 1024;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const size_t v = base + i * 256 + threadIdx.x;
+        if (v < nvec) out[v] = z;
+    }
+    if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < tail_bytes) tail[threadIdx.x] = 0;
+}
+
+// One thread per (n,t,u) row; rows outside t < lx, u <= ly stay zero.
+template <typename OutT>
+__global__ void __launch_bounds__(256) k_dense_patch(const DenseArgs a, int64_t rows) {
+    const int U = a.U1 - 1, V = a.V;
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < rows;
+         r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t nt = r / a.U1;
+        const int u = static_cast<int>(r - nt * a.U1);
+        const int n = static_cast<int>(nt / a.T);
+        const int t = static_cast<int>(nt - static_cast<int64_t>(n) * a.T);
+        const int lx_n = a.lx[n];
+        const int Un = min(a.ly[n], U);
+        if (t >= min(lx_n, a.T) || u > Un) continue;
+        const float go = a.scalar_grad ? a.grad_out[0] * utterance_weight(a.red, lx_n) : a.grad_out[n];
+        const int *y = a.ys + static_cast<int64_t>(n) * U;
+        const int y_prev = (u >= 1) ? y[u - 1] : 0;
+        const int y_next = (u < Un) ? y[u] : 0;
+        const RowPatch<OutT> p = make_patch<OutT>(a.GR[r], go, y_prev, y_next, u, Un, V);
+        OutT *row = static_cast<OutT *>(a.out) + r * V;
+        row[0] = p.c0;
+        if (p.i1 >= 0) row[p.i1] = p.c1;
+        if (p.i2 >= 0) row[p.i2] = p.c2;
     }
 }
 
