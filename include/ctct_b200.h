@@ -127,8 +127,21 @@ int ctct_b200_loss_backward_reduced(const float *grads3, const float *grad_loss,
                                     void *dense, void *stream);
 
 /*
+ * Most fused form of the forward pass: reduction 0 (none; `loss` unused), 1 ('sum') or 2 ('mean')
+ * as above, plus an optional buffer (`clear`, `clear_bytes`, 16-byte aligned) that is filled with
+ * zeros by extra thread blocks of the lattice launch.  Passing the dense gradient buffer here
+ * moves its HBM-bound clearing under the latency-bound lattice; the backward pass is then
+ * ctct_b200_loss_backward_patch instead of ctct_b200_loss_backward[_reduced].
+ */
+int ctct_b200_loss_forward_fused(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx,
+                                 const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
+                                 int want_grad, int reduction, int average_frames, float norm,
+                                 float *costs, float *loss, float *grads3, void *clear, size_t clear_bytes,
+                                 void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * Two-step form of the dense gradient, for callers that can clear the buffer early (before the
- * gradient scale exists, e.g. on a second stream while the latency-bound lattice runs):
+ * gradient scale exists; ctct_b200_loss_forward_fused does the clearing inside the lattice launch):
  *   ctct_b200_zero_fill            streams zeros over `bytes` bytes (16-byte aligned buffer);
  *   ctct_b200_loss_backward_patch  writes the <= 3 non-zero columns of every live row into a
  *                                  buffer that is already zero.

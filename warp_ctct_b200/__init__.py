@@ -30,38 +30,107 @@ def _require_cuda(**tensors) -> None:
 
 
 def _as_int(t: T) -> T:
+    if t.dtype == torch.int32 and t.is_contiguous():
+        return t
     return t.to(torch.int32).contiguous()
 
 
 # The dense gradient is zero except for <= 3 columns per row, and clearing it needs nothing the
-# forward pass computes.  With PREZERO on, the forward pass allocates the gradient and clears it on
-# a second stream while the (latency-bound) lattice runs; the backward pass then only patches the
-# non-zero columns.  Off (or for small tensors, or on a second backward through the same graph)
-# the backward pass writes the whole tensor in one pass.  Set CTCT_B200_PREZERO=0 to turn it off.
+# forward pass computes.  With PREZERO on, the forward pass allocates the gradient and has it
+# cleared by extra thread blocks of the (latency-bound) lattice launch; the backward pass then
+# only patches the non-zero columns.  Off (or for small tensors, or on a second backward through
+# the same graph) the backward pass writes the whole tensor in one pass.
+# Set CTCT_B200_PREZERO=0 to turn it off.
 PREZERO = os.environ.get("CTCT_B200_PREZERO", "1") != "0"
 PREZERO_MIN_BYTES = 8 << 20
-_side_streams = {}
+_ELEM_SIZE = {torch.float32: 4, torch.float16: 2, torch.bfloat16: 2}
+_size_cache = {}
 
 
-def _start_prezero(dev, shape, dtype):
-    """Allocate the dense gradient and start clearing it on the side stream of ``dev``.
-    Returns (tensor, event recorded after the clear) or None when pre-clearing is not worthwhile."""
-    nbytes = torch.empty((), dtype=dtype).element_size()
-    for d in shape:
-        nbytes *= d
-    if not PREZERO or nbytes < PREZERO_MIN_BYTES or torch.cuda.is_current_stream_capturing():
-        return None
-    cur = torch.cuda.current_stream(dev)
-    side = _side_streams.get(dev.index)
-    if side is None:
-        side = _side_streams[dev.index] = torch.cuda.Stream(dev)
-    dense = torch.empty(shape, dtype=dtype, device=dev)
-    side.wait_stream(cur)  # whatever used this memory before was enqueued on the current stream
-    _lib.check(_lib.lib().ctct_b200_zero_fill(dense.data_ptr(), nbytes, side.cuda_stream), "ctct_b200_zero_fill")
-    done = torch.cuda.Event()
-    done.record(side)
-    dense.record_stream(side)
-    return dense, done
+def _sizes(N: int, Tm: int, U1: int, want_grad: bool):
+    """(bytes of the compact gradient rounded up to 256, workspace bytes), cached per shape."""
+    key = (N, Tm, U1, want_grad)
+    hit = _size_cache.get(key)
+    if hit is None:
+        lib = _lib.lib()
+        ws = lib.ctct_b200_workspace_bytes(N, Tm, U1, int(want_grad))
+        if ws == 0 and N > 0:
+            raise RuntimeError(f"unsupported problem size N={N}, T={Tm}, U+1={U1}")
+        g3 = (lib.ctct_b200_grads3_elems(N, Tm, U1) * 4 + 255) // 256 * 256 if want_grad else 0
+        hit = _size_cache[key] = (g3, max(ws, 256))
+    return hit
+
+
+def _fused_forward(ctx, log_probs: T, labels: T, lx: T, ly: T, requires_grad: bool, red: int, average_frames: bool,
+                   norm: float):
+    """Shared forward of the two fused autograd functions: one C-ABI call (gather, lattice with the
+    gradient buffer cleared on the side, occupancy gradient, optional reduction).
+    Returns the float32 tensor [loss, costs[0..N)]."""
+    N, Tm, U1, V = log_probs.shape
+    dev = log_probs.device
+    lib = _lib.lib()
+    g3_bytes, ws_bytes = _sizes(N, Tm, U1, requires_grad)
+    switch = torch.cuda.current_device() != dev.index
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
+        out = torch.empty((N + 1,), dtype=torch.float32, device=dev)
+        # one allocation: [compact gradient | workspace]; kept until the backward pass
+        buf = torch.empty((g3_bytes + ws_bytes,), dtype=torch.uint8, device=dev)
+        dense = None
+        nbytes = N * Tm * U1 * V * _ELEM_SIZE[log_probs.dtype]
+        if requires_grad and PREZERO and nbytes >= PREZERO_MIN_BYTES:
+            dense = torch.empty((N, Tm, U1, V), dtype=log_probs.dtype, device=dev)
+        base = buf.data_ptr()
+        rc = lib.ctct_b200_loss_forward_fused(
+            log_probs.data_ptr(), _lib.dtype_code(log_probs.dtype), labels.data_ptr(), lx.data_ptr(), ly.data_ptr(),
+            N, Tm, U1, V, int(requires_grad), red, int(average_frames), norm, out.data_ptr() + 4, out.data_ptr(),
+            base if requires_grad else None, dense.data_ptr() if dense is not None else None,
+            nbytes if dense is not None else 0, base + g3_bytes, ws_bytes, torch._C._cuda_getCurrentRawStream(dev.index))
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
+    _lib.check(rc, "ctct_b200_loss_forward_fused")
+    if requires_grad:
+        ctx.save_for_backward(buf, labels, lx, ly)
+        ctx.meta = (N, Tm, U1, V, log_probs.dtype, red, bool(average_frames), float(norm))
+        ctx.cleared = dense
+    return out
+
+
+def _fused_backward(ctx, grad: T):
+    """Shared backward: dense (N,T,U+1,V) gradient; `grad` is (N,) when red == 0, else a scalar."""
+    buf, labels, lx, ly = ctx.saved_tensors
+    N, Tm, U1, V, dtype, red, avg, norm = ctx.meta
+    dev = buf.device
+    lib = _lib.lib()
+    go = grad.to(torch.float32).contiguous()
+    dense, ctx.cleared = ctx.cleared, None
+    switch = torch.cuda.current_device() != dev.index
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
+        st = torch._C._cuda_getCurrentRawStream(dev.index)
+        if dense is not None:  # cleared during the forward pass: patch the non-zero columns
+            rc = lib.ctct_b200_loss_backward_patch(buf.data_ptr(), go.data_ptr(), int(red != 0), red, int(avg), norm,
+                                                   labels.data_ptr(), lx.data_ptr(), ly.data_ptr(), N, Tm, U1, V,
+                                                   _lib.dtype_code(dtype), dense.data_ptr(), st)
+        else:
+            dense = torch.empty((N, Tm, U1, V), dtype=dtype, device=dev)
+            if red == 0:
+                rc = lib.ctct_b200_loss_backward(buf.data_ptr(), go.data_ptr(), labels.data_ptr(), lx.data_ptr(),
+                                                 ly.data_ptr(), N, Tm, U1, V, _lib.dtype_code(dtype), dense.data_ptr(), st)
+            else:
+                rc = lib.ctct_b200_loss_backward_reduced(buf.data_ptr(), go.data_ptr(), red, int(avg), norm,
+                                                         labels.data_ptr(), lx.data_ptr(), ly.data_ptr(), N, Tm, U1, V,
+                                                         _lib.dtype_code(dtype), dense.data_ptr(), st)
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
+    _lib.check(rc, "ctct_b200_loss_backward")
+    return dense
 
 
 class FusedCTCTLoss(torch.autograd.Function):
@@ -72,47 +141,11 @@ class FusedCTCTLoss(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, log_probs: T, labels: T, lx: T, ly: T, requires_grad: bool):
-        N, Tm, U1, V = log_probs.shape
-        dev = log_probs.device
-        lib = _lib.lib()
-        costs = torch.empty((N,), dtype=torch.float32, device=dev)
-        with torch.cuda.device(dev):
-            ctx.prezero = _start_prezero(dev, (N, Tm, U1, V), log_probs.dtype) if requires_grad else None
-            ws = _lib.workspace(N, Tm, U1, requires_grad, dev)
-            grads3 = None
-            if requires_grad:
-                grads3 = torch.empty((lib.ctct_b200_grads3_elems(N, Tm, U1),), dtype=torch.float32, device=dev)
-            rc = lib.ctct_b200_loss_forward(
-                _lib.ptr(log_probs), _lib.dtype_code(log_probs.dtype), _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
-                N, Tm, U1, V, int(requires_grad), _lib.ptr(costs), _lib.ptr(grads3), _lib.ptr(ws), ws.numel(),
-                _lib.stream_ptr(dev))
-        _lib.check(rc, "ctct_b200_loss_forward")
-        if requires_grad:
-            ctx.save_for_backward(grads3, labels, lx, ly)
-            ctx.meta = (N, Tm, U1, V, log_probs.dtype)
-        return costs
+        return _fused_forward(ctx, log_probs, labels, lx, ly, requires_grad, 0, False, 1.0)[1:]
 
     @staticmethod
     def backward(ctx, grad_outputs: T):
-        grads3, labels, lx, ly = ctx.saved_tensors
-        N, Tm, U1, V, dtype = ctx.meta
-        dev = grads3.device
-        go = grad_outputs.to(torch.float32).contiguous()
-        pre, ctx.prezero = ctx.prezero, None
-        with torch.cuda.device(dev):
-            if pre is not None:
-                dense, cleared = pre
-                torch.cuda.current_stream(dev).wait_event(cleared)
-                rc = _lib.lib().ctct_b200_loss_backward_patch(
-                    _lib.ptr(grads3), _lib.ptr(go), 0, 0, 0, 1.0, _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
-                    N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
-            else:
-                dense = torch.empty((N, Tm, U1, V), dtype=dtype, device=dev)
-                rc = _lib.lib().ctct_b200_loss_backward(
-                    _lib.ptr(grads3), _lib.ptr(go), _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
-                    N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
-        _lib.check(rc, "ctct_b200_loss_backward")
-        return dense, None, None, None, None
+        return _fused_backward(ctx, grad_outputs), None, None, None, None
 
 
 class FusedCTCTLossReduced(torch.autograd.Function):
@@ -123,48 +156,12 @@ class FusedCTCTLossReduced(torch.autograd.Function):
     @staticmethod
     def forward(ctx, log_probs: T, labels: T, lx: T, ly: T, requires_grad: bool, mean: bool, average_frames: bool,
                 norm: float):
-        N, Tm, U1, V = log_probs.shape
-        dev = log_probs.device
-        lib = _lib.lib()
-        red = 2 if mean else 1
-        out = torch.empty((N + 1,), dtype=torch.float32, device=dev)  # [loss, costs...]
-        with torch.cuda.device(dev):
-            ctx.prezero = _start_prezero(dev, (N, Tm, U1, V), log_probs.dtype) if requires_grad else None
-            ws = _lib.workspace(N, Tm, U1, requires_grad, dev)
-            grads3 = None
-            if requires_grad:
-                grads3 = torch.empty((lib.ctct_b200_grads3_elems(N, Tm, U1),), dtype=torch.float32, device=dev)
-            rc = lib.ctct_b200_loss_forward_reduced(
-                _lib.ptr(log_probs), _lib.dtype_code(log_probs.dtype), _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly),
-                N, Tm, U1, V, int(requires_grad), red, int(bool(average_frames)), float(norm),
-                out.data_ptr() + 4, out.data_ptr(), _lib.ptr(grads3), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
-        _lib.check(rc, "ctct_b200_loss_forward_reduced")
-        if requires_grad:
-            ctx.save_for_backward(grads3, labels, lx, ly)
-            ctx.meta = (N, Tm, U1, V, log_probs.dtype, red, bool(average_frames), float(norm))
-        return out[0]
+        return _fused_forward(ctx, log_probs, labels, lx, ly, requires_grad, 2 if mean else 1, bool(average_frames),
+                              float(norm))[0]
 
     @staticmethod
     def backward(ctx, grad_loss: T):
-        grads3, labels, lx, ly = ctx.saved_tensors
-        N, Tm, U1, V, dtype, red, avg, norm = ctx.meta
-        dev = grads3.device
-        go = grad_loss.to(torch.float32).contiguous()
-        pre, ctx.prezero = ctx.prezero, None
-        with torch.cuda.device(dev):
-            if pre is not None:
-                dense, cleared = pre
-                torch.cuda.current_stream(dev).wait_event(cleared)
-                rc = _lib.lib().ctct_b200_loss_backward_patch(
-                    _lib.ptr(grads3), _lib.ptr(go), 1, red, int(avg), norm, _lib.ptr(labels), _lib.ptr(lx),
-                    _lib.ptr(ly), N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
-            else:
-                dense = torch.empty((N, Tm, U1, V), dtype=dtype, device=dev)
-                rc = _lib.lib().ctct_b200_loss_backward_reduced(
-                    _lib.ptr(grads3), _lib.ptr(go), red, int(avg), norm, _lib.ptr(labels), _lib.ptr(lx),
-                    _lib.ptr(ly), N, Tm, U1, V, _lib.dtype_code(dtype), _lib.ptr(dense), _lib.stream_ptr(dev))
-        _lib.check(rc, "ctct_b200_loss_backward_reduced")
-        return dense, None, None, None, None, None, None, None
+        return _fused_backward(ctx, grad_loss), None, None, None, None, None, None, None
 
 
 def ctct_loss_fwd(log_probs: T, ys: T, lx: T, ly: T, requires_grad: bool):

@@ -31,6 +31,8 @@ SIGNATURES = {
     "ctct_b200_loss_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "ctct_b200_loss_forward_reduced": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int, _int,
                                               C.c_float, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "ctct_b200_loss_forward_fused": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int, _int, C.c_float,
+                                            _vp, _vp, _vp, _vp, _sz, _vp, _sz, _vp]),
     "ctct_b200_loss_backward_reduced": (_int, [_vp, _vp, _int, _int, C.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
                                                _int, _vp, _vp]),
     "ctct_b200_zero_fill": (_int, [_vp, _sz, _vp]),

@@ -106,34 +106,51 @@ bool dims_ok(int64_t N, int64_t T, int64_t U1) {
 }
 
 template <int C>
-int launch_lattice_inst(const LatticeArgs &a, int N, int threads, size_t smem, cudaStream_t st) {
+int launch_lattice_inst(const LatticeArgs &a, unsigned grid, int block, size_t smem, cudaStream_t st) {
     if (smem > 48 * 1024) {
         if (cudaFuncSetAttribute(k_lattice<C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem)) != cudaSuccess)
             return check_launch("lattice smem attribute");
     }
-    dim3 grid(N, a.beta_only ? 1 : 2);
-    k_lattice<C><<<grid, threads, smem, st>>>(a);
+    k_lattice<C><<<grid, block, smem, st>>>(a);
     return check_launch("lattice");
 }
 
-int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st) {
+// `clear` / `clear_bytes`: optional buffer that extra blocks of the same launch fill with zeros
+int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st, void *clear = nullptr,
+                   size_t clear_bytes = 0) {
     if (N == 0) return CTCT_OK;
     const size_t rowbytes = static_cast<size_t>(a.U1) * sizeof(float4);
     int F = static_cast<int>((48 * 1024) / rowbytes);
     F = F < 1 ? 1 : (F > 16 ? 16 : F);
-    a.F = F;
     if (F > 1) F &= ~1;  // even, so that the frame parity is the same in every chunk
     a.F = F;
     const size_t smem = 2 * static_cast<size_t>(F) * rowbytes + 5 * 33 * sizeof(float);
     if (smem > 220 * 1024) return CTCT_ERR_UNSUPPORTED;
+    a.threads = cfg.threads;
+    a.lattice_blocks = N * (a.beta_only ? 1 : 2);
+    a.clear = nullptr;
+    a.clear_vecs = 0;
+    a.clear_tail = 0;
+    size_t zero_blocks = 0;
+    if (clear && clear_bytes) {
+        if (reinterpret_cast<uintptr_t>(clear) % 16) return CTCT_ERR_ARG;
+        a.clear = static_cast<uint4 *>(clear);
+        a.clear_vecs = clear_bytes / 16;
+        a.clear_tail = static_cast<int>(clear_bytes % 16);
+        zero_blocks = (a.clear_vecs + 1023) / 1024;
+        if (zero_blocks == 0) zero_blocks = 1;
+    }
+    if (zero_blocks + a.lattice_blocks > 0x7fffffffull) return CTCT_ERR_UNSUPPORTED;
+    const unsigned grid = static_cast<unsigned>(a.lattice_blocks + zero_blocks);
+    const int block = (zero_blocks && cfg.threads < 256) ? 256 : cfg.threads;
     switch (cfg.C) {
-    case 1: return launch_lattice_inst<1>(a, N, cfg.threads, smem, st);
-    case 2: return launch_lattice_inst<2>(a, N, cfg.threads, smem, st);
-    case 4: return launch_lattice_inst<4>(a, N, cfg.threads, smem, st);
-    case 8: return launch_lattice_inst<8>(a, N, cfg.threads, smem, st);
-    case 16: return launch_lattice_inst<16>(a, N, cfg.threads, smem, st);
-    case 32: return launch_lattice_inst<32>(a, N, cfg.threads, smem, st);
+    case 1: return launch_lattice_inst<1>(a, grid, block, smem, st);
+    case 2: return launch_lattice_inst<2>(a, grid, block, smem, st);
+    case 4: return launch_lattice_inst<4>(a, grid, block, smem, st);
+    case 8: return launch_lattice_inst<8>(a, grid, block, smem, st);
+    case 16: return launch_lattice_inst<16>(a, grid, block, smem, st);
+    case 32: return launch_lattice_inst<32>(a, grid, block, smem, st);
     }
     return CTCT_ERR_UNSUPPORTED;
 }
@@ -280,7 +297,11 @@ int launch_patch_t(const DenseArgs &a, int64_t N, cudaStream_t st) {
     if (rows == 0) return CTCT_OK;
     const int64_t want = (rows + 255) / 256;
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
-    k_dense_patch<OutT><<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(a, rows);
+    const bool sectors = (static_cast<int64_t>(a.V) * sizeof(OutT)) % 32 == 0 && reinterpret_cast<uintptr_t>(a.out) % 32 == 0;
+    if (sectors)
+        k_dense_patch<OutT, true><<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(a, rows);
+    else
+        k_dense_patch<OutT, false><<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(a, rows);
     return check_launch("dense_patch");
 }
 
@@ -310,7 +331,8 @@ int dense_backward(DenseArgs a, int64_t N, int dtype, void *stream) {
 // gather -> lattice -> occupancy gradient (+ optional reduction of the costs into *loss_out)
 int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
                  int64_t T, int64_t U1, int64_t V, int want_grad, float *costs, float *grads3, void *workspace,
-                 size_t workspace_bytes, void *stream, float *loss_out, ReduceSpec red) {
+                 size_t workspace_bytes, void *stream, float *loss_out, ReduceSpec red, void *clear = nullptr,
+                 size_t clear_bytes = 0) {
     if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
     if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
     if (N == 0) return CTCT_OK;
@@ -326,7 +348,7 @@ int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int3
     int rc = launch_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float *>(ws + w.G), N, T, U1, V, true, 1, st);
     if (rc) return rc;
     prof_mark(slot, 1, st);
-    rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st);
+    rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st, clear, clear_bytes);
     if (rc) return rc;
     prof_mark(slot, 2, st);
     if (want_grad) {
@@ -384,6 +406,18 @@ int ctct_b200_loss_forward_reduced(const void *log_probs, int dtype, const int32
     if ((reduction != 1 && reduction != 2) || !loss || !(norm > 0.0f)) return CTCT_ERR_ARG;
     return forward_impl(log_probs, dtype, ys, lx, ly, N, T, U1, V, want_grad, costs, grads3, workspace, workspace_bytes,
                         stream, loss, ReduceSpec{reduction, average_frames ? 1 : 0, norm});
+}
+
+int ctct_b200_loss_forward_fused(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx,
+                                 const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int want_grad,
+                                 int reduction, int average_frames, float norm, float *costs, float *loss,
+                                 float *grads3, void *clear, size_t clear_bytes, void *workspace,
+                                 size_t workspace_bytes, void *stream) {
+    if (reduction < 0 || reduction > 2) return CTCT_ERR_ARG;
+    if (reduction != 0 && (!loss || !(norm > 0.0f))) return CTCT_ERR_ARG;
+    return forward_impl(log_probs, dtype, ys, lx, ly, N, T, U1, V, want_grad, costs, grads3, workspace, workspace_bytes,
+                        stream, reduction ? loss : nullptr, ReduceSpec{reduction, average_frames ? 1 : 0, reduction ? norm : 1.0f},
+                        clear, clear_bytes);
 }
 
 int ctct_b200_loss_backward_reduced(const float *grads3, const float *grad_loss, int reduction, int average_frames,

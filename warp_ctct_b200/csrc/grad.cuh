@@ -331,9 +331,40 @@ __global__ void __launch_bounds__(256) k_zero_fill(uint4 *__restrict__ out, size
     if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < tail_bytes) tail[threadIdx.x] = 0;
 }
 
-// One thread per (n,t,u) row; rows outside t < lx, u <= ly stay zero.
+// Writes one whole 32-byte sector of a row: zeros except the patched columns that fall into it.
+// Whole-sector writes need no read of the old contents, so patching costs DRAM writes only.
 template <typename OutT>
+__device__ __forceinline__ void write_sector(OutT *row, int sector, const RowPatch<OutT> &p) {
+    constexpr int E = OutOps<OutT>::E;  // elements per 16 bytes
+    uint4 w[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        unsigned b[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const int col = sector * 2 * E + h * E + e;
+            OutT x = OutOps<OutT>::cvt(0.0f);
+            if (col == 0) x = p.c0;
+            if (col == p.i1) x = p.c1;
+            if (col == p.i2) x = p.c2;
+            b[e] = out_bits<OutT>(x);
+        }
+        if constexpr (E == 4) {
+            w[h] = make_uint4(b[0], b[1], b[2], b[3]);
+        } else {
+            w[h] = make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16));
+        }
+    }
+    uint4 *dst = reinterpret_cast<uint4 *>(row) + sector * 2;
+    dst[0] = w[0];
+    dst[1] = w[1];
+}
+
+// One thread per (n,t,u) row; rows outside t < lx, u <= ly stay zero.  SECTORS: rows start on
+// 32-byte boundaries and V is a multiple of the sector width.
+template <typename OutT, bool SECTORS>
 __global__ void __launch_bounds__(256) k_dense_patch(const DenseArgs a, int64_t rows) {
+    constexpr int ES = 2 * OutOps<OutT>::E;  // elements per 32-byte sector
     const int U = a.U1 - 1, V = a.V;
     for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < rows;
          r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -350,9 +381,16 @@ __global__ void __launch_bounds__(256) k_dense_patch(const DenseArgs a, int64_t 
         const int y_next = (u < Un) ? y[u] : 0;
         const RowPatch<OutT> p = make_patch<OutT>(a.GR[r], go, y_prev, y_next, u, Un, V);
         OutT *row = static_cast<OutT *>(a.out) + r * V;
-        row[0] = p.c0;
-        if (p.i1 >= 0) row[p.i1] = p.c1;
-        if (p.i2 >= 0) row[p.i2] = p.c2;
+        if (SECTORS) {
+            const int s1 = p.i1 >= 0 ? p.i1 / ES : 0, s2 = p.i2 >= 0 ? p.i2 / ES : 0;
+            write_sector<OutT>(row, 0, p);
+            if (s1 != 0) write_sector<OutT>(row, s1, p);
+            if (s2 != 0 && s2 != s1) write_sector<OutT>(row, s2, p);
+        } else {
+            row[0] = p.c0;
+            if (p.i1 >= 0) row[p.i1] = p.c1;
+            if (p.i2 >= 0) row[p.i2] = p.c2;
+        }
     }
 }
 

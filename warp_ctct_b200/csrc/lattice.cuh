@@ -45,7 +45,15 @@ struct LatticeArgs {
     float *costs;        // [N]
     int T, U1, F;
     int beta_only;       // 1: only the backward variable (no gradient wanted), no table stores
+    int threads;         // threads of one lattice CTA (multiple of 32, <= blockDim.x)
+    int lattice_blocks;  // blocks [0, lattice_blocks) run the lattice, the rest clear `clear`
+    uint4 *clear;        // optional buffer to fill with zeros while the lattice runs (or nullptr)
+    unsigned long long clear_vecs;  // 16-byte vectors in `clear`
+    int clear_tail;      // bytes after the last full vector
 };
+
+// barrier among the first `nthreads` threads of the block (named barrier 1)
+__device__ __forceinline__ void cta_sync(int nthreads) { asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory"); }
 
 constexpr int RENORM = 2;  // frames between renormalisations
 
@@ -61,10 +69,10 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
     constexpr unsigned FULL = 0xffffffffu;
     constexpr int H = MULTI ? (C == 1 ? 2 : 1) : 0;
     constexpr int REAL_LANES = 32 - H;
-    const int n = blockIdx.x;
+    const int n = a.beta_only ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x >> 1);
     const bool store = !a.beta_only;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int NT = blockDim.x, W = NT >> 5;
+    const int NT = a.threads, W = NT >> 5;  // threads of the lattice role (the block may be wider)
     const int U1 = a.U1, F = a.F, T = a.T;
     const int U = U1 - 1, S2 = 2 * U1;  // number of slots
     const int Tn = max(0, min(a.lx[n], T));
@@ -133,7 +141,7 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
     if (MULTI) {
         for (int i = tid; i < 4 * (W + 1); i += NT) xs[i] = NEG;
         for (int i = tid; i < W + 1; i += NT) xo[i] = 0;
-        __syncthreads();
+        cta_sync(NT);
         // publish the starting values so that the first halo load sees them
         if (DIR == 0) {
             if (C == 1) {
@@ -150,7 +158,7 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
                 xs[(0 * (W + 1) + e_pub) * 2 + 1] = x[C >= 2 ? 1 : 0];
             }
         }
-        __syncthreads();
+        cta_sync(NT);
     }
     float adj = 0.0f;        // neighbour warp's offset minus ours
     bool untouched = true;   // no state of this warp reachable yet (as of the last renormalisation)
@@ -276,7 +284,7 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
                 }
             }
             if (renorm && off_publisher) xo[e_pub] = off;
-            __syncthreads();
+            cta_sync(NT);
         }
         constexpr int tstep = (DIR == 0) ? 1 : -1;
         row += tstep * 4 * U1;
@@ -296,7 +304,7 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
             cp_async_wait<0>();
         }
         if (MULTI)
-            __syncthreads();
+            cta_sync(NT);
         else
             __syncwarp();
         int lo, hi;
@@ -320,7 +328,7 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
         }
         frame += nf;
         if (MULTI)
-            __syncthreads();
+            cta_sync(NT);
         else
             __syncwarp();
     }
@@ -353,11 +361,29 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
     }
 }
 
+// One launch, two roles.  Blocks [0, lattice_blocks) are the lattice CTAs (utterance n = block / 2,
+// direction = block & 1; they are dispatched first).  The remaining blocks stream zeros over
+// `clear` -- the dense gradient buffer of the backward pass, which needs nothing the forward pass
+// computes -- 1024 16-byte vectors each, so that the HBM-bound clearing runs on the SMs the
+// latency-bound lattice leaves idle instead of costing its own 150 us later.
 template <int C>
 __global__ void __launch_bounds__(1024) k_lattice(const LatticeArgs a) {
     extern __shared__ __align__(16) float4 smem4[];
-    const int dir = a.beta_only ? 1 : static_cast<int>(blockIdx.y);
-    const bool multi = blockDim.x > 32;
+    if (static_cast<int>(blockIdx.x) >= a.lattice_blocks) {
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+        const unsigned long long chunk = blockIdx.x - a.lattice_blocks;
+        const unsigned long long base = chunk * 1024ull;
+        for (unsigned i = threadIdx.x; i < 1024u; i += blockDim.x) {
+            const unsigned long long v = base + i;
+            if (v < a.clear_vecs) a.clear[v] = z;
+        }
+        if (chunk == 0 && static_cast<int>(threadIdx.x) < a.clear_tail)
+            reinterpret_cast<unsigned char *>(a.clear + a.clear_vecs)[threadIdx.x] = 0;
+        return;
+    }
+    if (static_cast<int>(threadIdx.x) >= a.threads) return;
+    const int dir = a.beta_only ? 1 : static_cast<int>(blockIdx.x & 1);
+    const bool multi = a.threads > 32;
     if (dir == 0) {
         if (multi)
             lattice_run<C, 0, true>(a, smem4);
