@@ -82,4 +82,66 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// A slice of a buffer that extra thread blocks of a kernel fill with zeros while the kernel's own
+// blocks do their work.  The dense gradient of the backward pass is all zeros but for <= 3
+// columns per row, and clearing it needs nothing the forward pass computes, so the forward
+// kernels carry its clearing: blocks [first_block, gridDim.x) of a launch clear 1024 16-byte
+// vectors each (many short blocks reach the HBM write peak, a persistent grid does not).
+struct ClearSlice {
+    uint4 *ptr;                 // nullptr: no clearing in this launch
+    unsigned long long vecs;    // 16-byte vectors in this slice
+    int tail;                   // extra bytes after the last vector (only on the final slice)
+    unsigned first_block;       // blocks below this index do the kernel's own work
+};
+
+constexpr unsigned CLEAR_TILE_BYTES = 16384;                       // zeroed shared-memory tile
+constexpr unsigned CLEAR_TILES_PER_BLOCK = 16;                     // bulk stores per clearing block
+constexpr unsigned CLEAR_CHUNK = CLEAR_TILE_BYTES / 16 * CLEAR_TILES_PER_BLOCK;  // 16-byte vectors per block
+
+// Returns true if this block is a clearing block (and has done its clearing).
+// The block zeroes a 16 KB tile of its shared memory once and one thread then streams it out with
+// 1-D bulk (TMA) stores: a handful of instructions per 256 KB, so the clearing hardly touches the
+// load/store pipes that the kernel's own blocks on the same SM depend on.  `smem` must offer
+// CLEAR_TILE_BYTES (16-byte aligned); with less, plain 16-byte stores are used.
+__device__ __forceinline__ bool clear_role(const ClearSlice &c, void *smem, unsigned smem_bytes) {
+    if (c.ptr == nullptr || blockIdx.x < c.first_block) return false;
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    const unsigned long long chunk = blockIdx.x - c.first_block;
+    const unsigned long long base = chunk * CLEAR_CHUNK;
+    uint4 *p = c.ptr + base;
+    const unsigned long long left = c.vecs > base ? c.vecs - base : 0;
+    const unsigned n = left < CLEAR_CHUNK ? static_cast<unsigned>(left) : CLEAR_CHUNK;
+    if (chunk == 0 && static_cast<int>(threadIdx.x) < c.tail) reinterpret_cast<unsigned char *>(c.ptr + c.vecs)[threadIdx.x] = 0;
+    if (smem_bytes >= CLEAR_TILE_BYTES) {
+        uint4 *tile = static_cast<uint4 *>(smem);
+        for (unsigned i = threadIdx.x; i < CLEAR_TILE_BYTES / 16; i += blockDim.x) tile[i] = z;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> async proxy reads
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned src = static_cast<unsigned>(__cvta_generic_to_shared(tile));
+            unsigned done = 0;
+            while (done < n) {
+                const unsigned v = (n - done) < CLEAR_TILE_BYTES / 16 ? (n - done) : CLEAR_TILE_BYTES / 16;
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(p + done), "r"(src),
+                             "r"(v * 16u)
+                             : "memory");
+                done += v;
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the tile must outlive the reads
+        }
+        return true;
+    }
+    const unsigned nt = blockDim.x;
+    unsigned i = threadIdx.x;
+    for (; i + 3 * nt < n; i += 4 * nt) {  // four independent stores in flight per thread
+        p[i] = z;
+        p[i + nt] = z;
+        p[i + 2 * nt] = z;
+        p[i + 3 * nt] = z;
+    }
+    for (; i < n; i += nt) p[i] = z;
+    return true;
+}
+
 }  // namespace ctct

@@ -105,93 +105,130 @@ bool dims_ok(int64_t N, int64_t T, int64_t U1) {
            N * T * U1 < (int64_t(1) << 38);
 }
 
-template <int C>
+const ClearSlice kNoClear = {nullptr, 0, 0, 0};
+
+// number of clearing blocks a slice adds to a launch
+unsigned clear_blocks(const ClearSlice &c) {
+    if (!c.ptr) return 0;
+    const unsigned long long b = (c.vecs + CLEAR_CHUNK - 1) / CLEAR_CHUNK;
+    return static_cast<unsigned>(b ? b : 1);
+}
+
+// Split the buffer to clear over the three forward launches (gather, lattice, occupancy gradient).
+// Measured at the benchmark shape: clearing beside the gather or the occupancy gradient gains
+// nothing (both are bound by the rate of isolated DRAM accesses and slow down by as much as the
+// clearing they host), clearing beside the lattice is free (the lattice is bound by its own
+// dependent instruction stream).  So the lattice launch takes everything; the split stays
+// parametric.  Slices are whole chunks, the last one takes the remainder and the tail.
+void plan_clear(void *clear, size_t bytes, ClearSlice out[3]) {
+    out[0] = out[1] = out[2] = kNoClear;
+    if (!clear || !bytes) return;
+    const unsigned long long vecs = bytes / 16;
+    const unsigned long long chunks = (vecs + CLEAR_CHUNK - 1) / CLEAR_CHUNK;
+    const unsigned long long c0 = 0, c2 = 0;
+    const unsigned long long c1 = chunks - c0 - c2;
+    uint4 *p = static_cast<uint4 *>(clear);
+    unsigned long long done = 0;
+    const unsigned long long share[3] = {c0, c1, c2};
+    for (int i = 0; i < 3; ++i) {
+        unsigned long long v = share[i] * CLEAR_CHUNK;
+        if (done + v > vecs || i == 2) v = vecs - done;
+        if (share[i] == 0 && i != 2) continue;
+        out[i].ptr = p + done;
+        out[i].vecs = v;
+        out[i].tail = 0;
+        done += v;
+    }
+    out[2].tail = static_cast<int>(bytes % 16);
+    if (out[2].vecs == 0 && out[2].tail == 0) out[2] = kNoClear;
+}
+
+template <int C, int MAXT, int MINB>
 int launch_lattice_inst(const LatticeArgs &a, unsigned grid, int block, size_t smem, cudaStream_t st) {
     if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(k_lattice<C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(k_lattice<C, MAXT, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem)) != cudaSuccess)
             return check_launch("lattice smem attribute");
     }
-    k_lattice<C><<<grid, block, smem, st>>>(a);
+    k_lattice<C, MAXT, MINB><<<grid, block, smem, st>>>(a);
     return check_launch("lattice");
 }
 
-// `clear` / `clear_bytes`: optional buffer that extra blocks of the same launch fill with zeros
-int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st, void *clear = nullptr,
-                   size_t clear_bytes = 0) {
+// `clear`: optional slice that extra blocks of the same launch fill with zeros
+int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st, ClearSlice clear = kNoClear) {
     if (N == 0) return CTCT_OK;
     const size_t rowbytes = static_cast<size_t>(a.U1) * sizeof(float4);
     int F = static_cast<int>((48 * 1024) / rowbytes);
-    F = F < 1 ? 1 : (F > 16 ? 16 : F);
+    const int fmax = 16;
+    F = F < 1 ? 1 : (F > fmax ? fmax : F);
     if (F > 1) F &= ~1;  // even, so that the frame parity is the same in every chunk
     a.F = F;
-    const size_t smem = 2 * static_cast<size_t>(F) * rowbytes + 5 * 33 * sizeof(float);
+    size_t smem = 2 * static_cast<size_t>(F) * rowbytes + 5 * 33 * sizeof(float);
+    if (clear.ptr && smem < CLEAR_TILE_BYTES) smem = CLEAR_TILE_BYTES;  // room for the clearing blocks' zero tile
     if (smem > 220 * 1024) return CTCT_ERR_UNSUPPORTED;
+    a.smem_bytes = static_cast<unsigned>(smem);
     a.threads = cfg.threads;
-    a.lattice_blocks = N * (a.beta_only ? 1 : 2);
-    a.clear = nullptr;
-    a.clear_vecs = 0;
-    a.clear_tail = 0;
-    size_t zero_blocks = 0;
-    if (clear && clear_bytes) {
-        if (reinterpret_cast<uintptr_t>(clear) % 16) return CTCT_ERR_ARG;
-        a.clear = static_cast<uint4 *>(clear);
-        a.clear_vecs = clear_bytes / 16;
-        a.clear_tail = static_cast<int>(clear_bytes % 16);
-        zero_blocks = (a.clear_vecs + 1023) / 1024;
-        if (zero_blocks == 0) zero_blocks = 1;
-    }
-    if (zero_blocks + a.lattice_blocks > 0x7fffffffull) return CTCT_ERR_UNSUPPORTED;
-    const unsigned grid = static_cast<unsigned>(a.lattice_blocks + zero_blocks);
+    const unsigned own = static_cast<unsigned>(N) * (a.beta_only ? 1 : 2);
+    const unsigned zero_blocks = clear_blocks(clear);
+    clear.first_block = own;
+    a.clear = clear;
+    if (static_cast<unsigned long long>(own) + zero_blocks > 0x7fffffffull) return CTCT_ERR_UNSUPPORTED;
+    const unsigned grid = own + zero_blocks;
     const int block = (zero_blocks && cfg.threads < 256) ? 256 : cfg.threads;
+    // up to 512 threads the kernel is held to 40 registers, so that the clearing blocks of the
+    // same launch reach a high occupancy (they need many stores in flight, not registers)
+    if (cfg.C == 1 && block <= 512) return launch_lattice_inst<1, 512, 3>(a, grid, block, smem, st);
     switch (cfg.C) {
-    case 1: return launch_lattice_inst<1>(a, grid, block, smem, st);
-    case 2: return launch_lattice_inst<2>(a, grid, block, smem, st);
-    case 4: return launch_lattice_inst<4>(a, grid, block, smem, st);
-    case 8: return launch_lattice_inst<8>(a, grid, block, smem, st);
-    case 16: return launch_lattice_inst<16>(a, grid, block, smem, st);
-    case 32: return launch_lattice_inst<32>(a, grid, block, smem, st);
+    case 1: return launch_lattice_inst<1, 1024, 1>(a, grid, block, smem, st);
+    case 2: return launch_lattice_inst<2, 1024, 1>(a, grid, block, smem, st);
+    case 4: return launch_lattice_inst<4, 1024, 1>(a, grid, block, smem, st);
+    case 8: return launch_lattice_inst<8, 1024, 1>(a, grid, block, smem, st);
+    case 16: return launch_lattice_inst<16, 1024, 1>(a, grid, block, smem, st);
+    case 32: return launch_lattice_inst<32, 1024, 1>(a, grid, block, smem, st);
     }
     return CTCT_ERR_UNSUPPORTED;
 }
 
 template <typename InT>
 int launch_gather_t(const void *lp, const int *ys, const int *lx, const int *ly, float *out, int64_t N,
-                    int64_t T, int64_t U1, int64_t V, bool internal, int valid_only, cudaStream_t st) {
+                    int64_t T, int64_t U1, int64_t V, bool internal, int valid_only, cudaStream_t st, ClearSlice clear) {
     const int64_t total = internal ? N * T * U1 * 4 : N * T * U1 * 3;
     if (total == 0) return CTCT_OK;
     const int64_t want = (total + 256 * 4 - 1) / (256 * 4);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
-    const int grid = static_cast<int>(want < cap ? want : cap);
+    const int own = static_cast<int>(want < cap ? want : cap);
+    clear.first_block = static_cast<unsigned>(own);
+    const unsigned grid = static_cast<unsigned>(own) + clear_blocks(clear);
     const InT *p = static_cast<const InT *>(lp);
-    const bool small = total < (int64_t(1) << 31) - int64_t(grid) * 256 * 4;
+    const bool small = total < (int64_t(1) << 31) - int64_t(own) * 256 * 4;
     if (internal) {
         if (small)
-            k_gather3<InT, unsigned, true><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only);
+            k_gather3<InT, unsigned, true><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only, clear);
         else
-            k_gather3<InT, unsigned long long, true><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only);
+            k_gather3<InT, unsigned long long, true><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only, clear);
     } else {
         if (small)
-            k_gather3<InT, unsigned, false><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only);
+            k_gather3<InT, unsigned, false><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only, clear);
         else
-            k_gather3<InT, unsigned long long, false><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only);
+            k_gather3<InT, unsigned long long, false><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only, clear);
     }
     return check_launch("gather");
 }
 
 int launch_gather(const void *lp, int dtype, const int *ys, const int *lx, const int *ly, float *out, int64_t N,
-                  int64_t T, int64_t U1, int64_t V, bool internal, int valid_only, cudaStream_t st) {
+                  int64_t T, int64_t U1, int64_t V, bool internal, int valid_only, cudaStream_t st,
+                  ClearSlice clear = kNoClear) {
     switch (dtype) {
-    case CTCT_F32: return launch_gather_t<float>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st);
-    case CTCT_F16: return launch_gather_t<__half>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st);
-    case CTCT_BF16: return launch_gather_t<__nv_bfloat16>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st);
+    case CTCT_F32: return launch_gather_t<float>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st, clear);
+    case CTCT_F16: return launch_gather_t<__half>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st, clear);
+    case CTCT_BF16: return launch_gather_t<__nv_bfloat16>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st, clear);
     }
     return CTCT_ERR_ARG;
 }
 
 int launch_fill_grad(const WsLayout &w, char *ws, const int *ys, const int *lx, const int *ly, float *out,
                      int ref_layout, int64_t N, int64_t T, int64_t U1, cudaStream_t st, const float *costs = nullptr,
-                     float *loss_out = nullptr, ReduceSpec red = ReduceSpec{0, 0, 1.0f}) {
+                     float *loss_out = nullptr, ReduceSpec red = ReduceSpec{0, 0, 1.0f}, ClearSlice clear = kNoClear) {
     if (N == 0) return CTCT_OK;
     if (T == 0) {
         if (loss_out) {
@@ -217,8 +254,12 @@ int launch_fill_grad(const WsLayout &w, char *ws, const int *ys, const int *lx, 
     g.U1 = (int)U1;
     g.ref_layout = ref_layout;
     const int cells = static_cast<int>(T * U1);
-    dim3 grid((cells + 255) / 256, (unsigned)N);
-    k_fill_grad<<<grid, 256, 0, st>>>(g);
+    g.blocks_per_utt = (cells + 255) / 256;
+    const unsigned long long own = static_cast<unsigned long long>(N) * g.blocks_per_utt;
+    if (own + clear_blocks(clear) > 0x7fffffffull) return CTCT_ERR_UNSUPPORTED;
+    clear.first_block = static_cast<unsigned>(own);
+    g.clear = clear;
+    k_fill_grad<<<static_cast<unsigned>(own) + clear_blocks(clear), 256, 0, st>>>(g);
     return check_launch("fill_grad");
 }
 
@@ -343,16 +384,20 @@ int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int3
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     char *ws = static_cast<char *>(workspace);
 
+    if (clear && reinterpret_cast<uintptr_t>(clear) % 16) return CTCT_ERR_ARG;
+    ClearSlice cs[3];
+    plan_clear(want_grad ? clear : nullptr, clear_bytes, cs);
+    if (!want_grad && clear && clear_bytes) cs[1] = ClearSlice{static_cast<uint4 *>(clear), clear_bytes / 16, static_cast<int>(clear_bytes % 16), 0};
     cudaEvent_t *slot = prof_slot(0);
     prof_mark(slot, 0, st);
-    int rc = launch_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float *>(ws + w.G), N, T, U1, V, true, 1, st);
+    int rc = launch_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float *>(ws + w.G), N, T, U1, V, true, 1, st, cs[0]);
     if (rc) return rc;
     prof_mark(slot, 1, st);
-    rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st, clear, clear_bytes);
+    rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st, cs[1]);
     if (rc) return rc;
     prof_mark(slot, 2, st);
     if (want_grad) {
-        rc = launch_fill_grad(w, ws, ys, lx, ly, grads3, 0, N, T, U1, st, costs, loss_out, red);
+        rc = launch_fill_grad(w, ws, ys, lx, ly, grads3, 0, N, T, U1, st, costs, loss_out, red, cs[2]);
     } else if (loss_out) {
         k_reduce_costs<<<1, 256, 0, st>>>(costs, lx, (int)N, red, loss_out);
         rc = check_launch("reduce_costs");

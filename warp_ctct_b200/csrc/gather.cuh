@@ -20,9 +20,10 @@ template <typename InT, typename IdxT, bool INTERNAL>
 __global__ void __launch_bounds__(256)
 k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__restrict__ lx,
           const int *__restrict__ ly, float *__restrict__ out, int T, int U1, int V,
-          IdxT total, int valid_only) {
+          IdxT total, int valid_only, const ClearSlice clear) {
+    if (clear_role(clear, nullptr, 0)) return;
     constexpr int PER = 4;
-    const IdxT stride = static_cast<IdxT>(gridDim.x) * blockDim.x;
+    const IdxT stride = static_cast<IdxT>(clear.ptr ? clear.first_block : gridDim.x) * blockDim.x;
     IdxT e0 = static_cast<IdxT>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int U = U1 - 1;
 

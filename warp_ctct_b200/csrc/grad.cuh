@@ -103,17 +103,20 @@ struct GradArgs {
     float *loss_out;
     int N;
     ReduceSpec red;
+    int blocks_per_utt;  // own blocks: N * blocks_per_utt, utterance n = block / blocks_per_utt
+    ClearSlice clear;
 };
 
-// One thread per (t,u) of one utterance (blockIdx.y).  Every arc (state at t) -> (state at
+// One thread per (t,u) of one utterance.  Every arc (state at t) -> (state at
 // t+1) contributes exp2(alpha + logp + beta - loglik); arcs outside the band contribute an
 // exact 0 because one of the two variables is "impossible" there, so the reference's band
 // guards (gather.cu:335-337,355-359) need no restating.
 __global__ void __launch_bounds__(256) k_fill_grad(const GradArgs a) {
-    if (a.loss_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0) reduce_costs_block(a.costs, a.lx, a.N, a.red, a.loss_out);
-    const int n = blockIdx.y;
+    if (clear_role(a.clear, nullptr, 0)) return;
+    if (a.loss_out != nullptr && blockIdx.x == 0) reduce_costs_block(a.costs, a.lx, a.N, a.red, a.loss_out);
+    const int n = blockIdx.x / a.blocks_per_utt;
     const int cells = a.T * a.U1;
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const int idx = (blockIdx.x - n * a.blocks_per_utt) * blockDim.x + threadIdx.x;
     if (idx >= cells) return;
     const int t = idx / a.U1;
     const int u = idx - t * a.U1;

@@ -46,10 +46,8 @@ struct LatticeArgs {
     int T, U1, F;
     int beta_only;       // 1: only the backward variable (no gradient wanted), no table stores
     int threads;         // threads of one lattice CTA (multiple of 32, <= blockDim.x)
-    int lattice_blocks;  // blocks [0, lattice_blocks) run the lattice, the rest clear `clear`
-    uint4 *clear;        // optional buffer to fill with zeros while the lattice runs (or nullptr)
-    unsigned long long clear_vecs;  // 16-byte vectors in `clear`
-    int clear_tail;      // bytes after the last full vector
+    ClearSlice clear;    // blocks from clear.first_block on zero a slice of the gradient buffer
+    unsigned smem_bytes; // dynamic shared memory of the launch
 };
 
 // barrier among the first `nthreads` threads of the block (named barrier 1)
@@ -361,26 +359,15 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
     }
 }
 
-// One launch, two roles.  Blocks [0, lattice_blocks) are the lattice CTAs (utterance n = block / 2,
-// direction = block & 1; they are dispatched first).  The remaining blocks stream zeros over
-// `clear` -- the dense gradient buffer of the backward pass, which needs nothing the forward pass
-// computes -- 1024 16-byte vectors each, so that the HBM-bound clearing runs on the SMs the
-// latency-bound lattice leaves idle instead of costing its own 150 us later.
-template <int C>
-__global__ void __launch_bounds__(1024) k_lattice(const LatticeArgs a) {
+// One launch, two roles.  The first blocks are the lattice CTAs (utterance n = block / 2,
+// direction = block & 1; they are dispatched first).  The remaining blocks stream zeros over a
+// slice of the dense gradient buffer of the backward pass (see ClearSlice), so that the
+// HBM-bound clearing runs on the SMs the latency-bound lattice leaves idle instead of costing
+// its own 150 us later.
+template <int C, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB) k_lattice(const LatticeArgs a) {
     extern __shared__ __align__(16) float4 smem4[];
-    if (static_cast<int>(blockIdx.x) >= a.lattice_blocks) {
-        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-        const unsigned long long chunk = blockIdx.x - a.lattice_blocks;
-        const unsigned long long base = chunk * 1024ull;
-        for (unsigned i = threadIdx.x; i < 1024u; i += blockDim.x) {
-            const unsigned long long v = base + i;
-            if (v < a.clear_vecs) a.clear[v] = z;
-        }
-        if (chunk == 0 && static_cast<int>(threadIdx.x) < a.clear_tail)
-            reinterpret_cast<unsigned char *>(a.clear + a.clear_vecs)[threadIdx.x] = 0;
-        return;
-    }
+    if (clear_role(a.clear, smem4, a.smem_bytes)) return;
     if (static_cast<int>(threadIdx.x) >= a.threads) return;
     const int dir = a.beta_only ? 1 : static_cast<int>(blockIdx.x & 1);
     const bool multi = a.threads > 32;
