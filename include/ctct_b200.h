@@ -207,6 +207,20 @@ int ctct_b200_log_matmul(const float *lhs, int64_t lhs_stride_b, int64_t lhs_str
                          int64_t B, int64_t M, int64_t K, int64_t N, float *out, void *stream);
 
 /*
+ * The same product for contiguous f (B,M,K) and g (B,N,K) -- den[b,i,j] = log sum_k exp(f[b,i,k] +
+ * g[b,j,k]), the denominator of ctct_simple_loss -- as a tensor-core GEMM on max-shifted
+ * exponentials (tcgen05 / TMEM / TMA, bf16 hi+lo operand split, fp32 accumulation) with the
+ * log / max rescaling in the epilogue.  Needs K % 8 == 0, K >= 64 and a scratch workspace of
+ * ctct_b200_log_matmul_tc_workspace_bytes (0 = shape not supported: use ctct_b200_log_matmul).
+ * Outputs whose shifted sum underflows (dynamic range beyond ~80 nats with maxima at different
+ * k) are detected on the device and recomputed by the exact kernel in the same call.
+ * Replaces log_matmul of csrc/binding.cpp:224-245 on the loss path (warp_ctct/__init__.py:195-200).
+ */
+size_t ctct_b200_log_matmul_tc_workspace_bytes(int64_t B, int64_t M, int64_t N, int64_t K);
+int ctct_b200_log_matmul_tc(const float *f, const float *g, int64_t B, int64_t M, int64_t N, int64_t K, float *den,
+                            void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * Backward of the product above for an arbitrary (signed) grad_out (B,M,N):
  *   grad_lhs[b,i,k]  = sum_j grad_out[b,i,j] * exp(lhs[b,i,k] + rhs[b,k,j] - res[b,i,j])
  *   grad_rhsT[b,j,k] = sum_i (same term)

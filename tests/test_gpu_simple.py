@@ -57,6 +57,40 @@ def test_log_matmul_matches_oracle(W, B, M, N, K):
     np.testing.assert_allclose(got2.cpu().numpy(), want, rtol=0, atol=2e-5)
 
 
+@pytest.mark.parametrize("B,M,N,K,scale", [(2, 130, 70, 256, 1.0), (3, 33, 17, 64, 2.0), (1, 257, 101, 4096, 1.0),
+                                           (2, 128, 128, 520, 3.0), (1, 300, 260, 136, 1.0)])
+def test_log_matmul_tensor_core_matches_oracle(W, B, M, N, K, scale):
+    """tcgen05 path: bf16 hi+lo operands, fp32 accumulation; the float64 oracle is the judge."""
+    from warp_ctct_b200.simple import log_matmul, log_matmul_tc
+    rng = np.random.default_rng(B * 7 + K)
+    f = (scale * rng.standard_normal((B, M, K))).astype(np.float32)
+    g = (scale * rng.standard_normal((B, N, K))).astype(np.float32)
+    f[0, 1, :] = -np.inf                       # dead row -> -inf outputs
+    want = oracle.log_matmul(f, g, np.float64)
+    f_t, g_t = _dev(f, g)
+    got = log_matmul_tc(f_t, g_t).cpu().numpy()
+    assert np.all(np.isneginf(got[0, 1])) and np.all(np.isneginf(want[0, 1]))
+    fin = np.isfinite(want)
+    np.testing.assert_allclose(got[fin], want[fin], rtol=1e-6, atol=5e-6)
+    exact = log_matmul(f_t, g_t.transpose(1, 2)).cpu().numpy()
+    np.testing.assert_allclose(got[fin], exact[fin], rtol=0, atol=2e-5)
+
+
+def test_log_matmul_tensor_core_falls_back_on_wide_range(W):
+    """Rows whose maxima sit at different k and are > 100 nats above the rest: the max-shifted
+    product underflows, the kernel notices and the exact kernel recomputes in the same call."""
+    from warp_ctct_b200.simple import log_matmul_tc
+    rng = np.random.default_rng(3)
+    B, M, N, K = 1, 40, 30, 128
+    f = rng.standard_normal((B, M, K)).astype(np.float32)
+    g = rng.standard_normal((B, N, K)).astype(np.float32)
+    f[0, 5, 3] += 300.0
+    g[0, 7, 90] += 300.0
+    want = oracle.log_matmul(f, g, np.float64)
+    got = log_matmul_tc(*_dev(f, g)).cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=2e-6, atol=2e-5)
+
+
 def test_log_matmul_extreme_values(W):
     from warp_ctct_b200.simple import log_matmul
     rng = np.random.default_rng(5)

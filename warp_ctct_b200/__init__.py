@@ -274,7 +274,7 @@ def ctct_loss(log_probs: torch.FloatTensor,
 
 
 from .simple import (FusedSimpleCTCTLoss, LogMMExp, SimpleCTCTLoss, ctct_loss_simple_fwd,  # noqa: E402,F401
-                     log_matmul, log_matmul_backward)
+                     log_matmul, log_matmul_backward, log_matmul_tc)
 
 
 def ctct_simple_loss(f: torch.FloatTensor,

@@ -10,6 +10,7 @@
 #include "grad.cuh"
 #include "lattice.cuh"
 #include "simple.cuh"
+#include "logmm_tc.cuh"
 
 using namespace ctct;
 
@@ -292,7 +293,8 @@ int launch_dense_t(DenseArgs a, int64_t N, cudaStream_t st) {
 }
 
 int launch_logmm(const float *lhs, int64_t lsb, int64_t lsi, int64_t lsk, const float *rhs, int64_t rsb, int64_t rsk,
-                 int64_t rsj, int64_t B, int64_t M, int64_t K, int64_t N, float *out, cudaStream_t st) {
+                 int64_t rsj, int64_t B, int64_t M, int64_t K, int64_t N, float *out, cudaStream_t st,
+                 const int *run_flags = nullptr) {
     if (B == 0 || M == 0 || N == 0) return CTCT_OK;
     LogmmArgs a;
     a.lhs = lhs;
@@ -307,9 +309,62 @@ int launch_logmm(const float *lhs, int64_t lsb, int64_t lsi, int64_t lsk, const 
     a.M = (int)M;
     a.K = (int)K;
     a.N = (int)N;
+    a.run_flags = run_flags;
     dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 31) / 32), (unsigned)B);
     k_logmm_exact<<<grid, 256, 0, st>>>(a);
     return check_launch("log_matmul");
+}
+
+// ---- tensor-core path -----------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// bf16 plane (B, rows, K), K contiguous -> 3-D tensor map with a 64 x 128 x 1 box, 128-byte swizzle
+bool make_plane_map(CUtensorMap *map, const void *ptr, int64_t B, int64_t rows, int64_t K) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)B};
+    const cuuint64_t gstride[2] = {(cuuint64_t)K * 2, (cuuint64_t)rows * K * 2};
+    const cuuint32_t box[3] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), gdim, gstride, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct TcLayout {
+    size_t ah, al, bh, bl, mf, mg, flags, total;
+};
+TcLayout tc_layout(int64_t B, int64_t M, int64_t N, int64_t K) {
+    TcLayout l;
+    size_t o = 0;
+    l.ah = o; o = align256(o + (size_t)B * M * K * 2);
+    l.al = o; o = align256(o + (size_t)B * M * K * 2);
+    l.bh = o; o = align256(o + (size_t)B * N * K * 2);
+    l.bl = o; o = align256(o + (size_t)B * N * K * 2);
+    l.mf = o; o = align256(o + (size_t)B * M * 4);
+    l.mg = o; o = align256(o + (size_t)B * N * 4);
+    l.flags = o; o = align256(o + 16);
+    l.total = o;
+    return l;
+}
+bool tc_shape_ok(int64_t B, int64_t M, int64_t N, int64_t K) {
+    return B >= 1 && B <= 65535 && M >= 1 && N >= 1 && K >= 64 && K % 8 == 0 && M < (int64_t(1) << 24) &&
+           N <= 65535 * (int64_t)TC_BN && K < (int64_t(1) << 30);
 }
 
 template <int VT>
@@ -628,6 +683,58 @@ int ctct_b200_log_matmul(const float *lhs, int64_t lsb, int64_t lsi, int64_t lsk
     if (B == 0 || M == 0 || N == 0) return CTCT_OK;
     if (!out || (K > 0 && (!lhs || !rhs))) return CTCT_ERR_ARG;
     return launch_logmm(lhs, lsb, lsi, lsk, rhs, rsb, rsk, rsj, B, M, K, N, out, static_cast<cudaStream_t>(stream));
+}
+
+
+size_t ctct_b200_log_matmul_tc_workspace_bytes(int64_t B, int64_t M, int64_t N, int64_t K) {
+    if (!tc_shape_ok(B, M, N, K)) return 0;
+    return tc_layout(B, M, N, K).total;
+}
+
+int ctct_b200_log_matmul_tc(const float *f, const float *g, int64_t B, int64_t M, int64_t N, int64_t K, float *den,
+                            void *workspace, size_t workspace_bytes, void *stream) {
+    if (!tc_shape_ok(B, M, N, K)) return CTCT_ERR_UNSUPPORTED;
+    if (!f || !g || !den) return CTCT_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(f) % 16 || reinterpret_cast<uintptr_t>(g) % 16) return CTCT_ERR_ARG;
+    const TcLayout l = tc_layout(B, M, N, K);
+    if (!workspace || workspace_bytes < l.total || reinterpret_cast<uintptr_t>(workspace) % 256) return CTCT_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char *ws = static_cast<char *>(workspace);
+    auto *ah = reinterpret_cast<__nv_bfloat16 *>(ws + l.ah), *al = reinterpret_cast<__nv_bfloat16 *>(ws + l.al);
+    auto *bh = reinterpret_cast<__nv_bfloat16 *>(ws + l.bh), *bl = reinterpret_cast<__nv_bfloat16 *>(ws + l.bl);
+    float *mf = reinterpret_cast<float *>(ws + l.mf), *mg = reinterpret_cast<float *>(ws + l.mg);
+    int *flags = reinterpret_cast<int *>(ws + l.flags);
+    CUtensorMap m_ah, m_al, m_bh, m_bl;
+    if (!make_plane_map(&m_ah, ah, B, M, K) || !make_plane_map(&m_al, al, B, M, K) ||
+        !make_plane_map(&m_bh, bh, B, N, K) || !make_plane_map(&m_bl, bl, B, N, K)) {
+        snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "cuTensorMapEncodeTiled failed");
+        return CTCT_ERR_LAUNCH;
+    }
+    if (cudaMemsetAsync(flags, 0, 16, st) != cudaSuccess) return check_launch("log_matmul_tc flags");
+    k_exp_split<<<static_cast<unsigned>(B * M), 256, 0, st>>>(f, (int)K, ah, al, mf);
+    int rc = check_launch("exp_split f");
+    if (rc) return rc;
+    k_exp_split<<<static_cast<unsigned>(B * N), 256, 0, st>>>(g, (int)K, bh, bl, mg);
+    rc = check_launch("exp_split g");
+    if (rc) return rc;
+    static std::once_flag attr_once;
+    std::call_once(attr_once, [] {
+        cudaFuncSetAttribute(k_logmm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+    });
+    LogmmTcArgs a;
+    a.den = den;
+    a.mf = mf;
+    a.mg = mg;
+    a.M = (int)M;
+    a.N = (int)N;
+    a.K = (int)K;
+    a.flags = flags;
+    dim3 grid((unsigned)((M + TC_BM - 1) / TC_BM), (unsigned)((N + TC_BN - 1) / TC_BN), (unsigned)B);
+    k_logmm_tc<<<grid, 128, TC_SMEM_BYTES, st>>>(m_ah, m_al, m_bh, m_bl, a);
+    rc = check_launch("log_matmul_tc");
+    if (rc) return rc;
+    // exact kernel, a no-op unless a wait ran out or a shifted sum underflowed
+    return launch_logmm(f, M * K, K, 1, g, N * K, 1, K, B, M, K, N, den, st, flags);
 }
 
 int ctct_b200_log_matmul_backward(const float *grad_out, const float *lhs, const float *rhsT, const float *res,

@@ -25,6 +25,7 @@ struct LogmmArgs {
     float *out;  // (B, M, N) contiguous
     int64_t lsb, lsi, lsk, rsb, rsk, rsj;
     int M, K, N;
+    const int *run_flags;  // optional {a, b}: run only if a or b is non-zero (fallback after the tensor-core kernel)
 };
 
 // 32x32 output tile per 256-thread block, 4 outputs per thread, K in chunks of 32 through
@@ -33,6 +34,7 @@ struct LogmmArgs {
 __global__ void __launch_bounds__(256) k_logmm_exact(const LogmmArgs a) {
     __shared__ float As[32][33];  // [i][k]
     __shared__ float Bs[32][33];  // [k][j]
+    if (a.run_flags != nullptr && a.run_flags[0] == 0 && a.run_flags[1] == 0) return;
     const int b = blockIdx.z;
     const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // ty in [0,8)

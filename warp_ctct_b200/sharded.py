@@ -43,10 +43,11 @@ class _AllReduceSum(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x: torch.Tensor, group):
-        y = x.clone()
+        # in place: the local partial sum is not needed by anything else
         if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
-        return y
+            dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
+        ctx.mark_dirty(x)
+        return x
 
     @staticmethod
     def backward(ctx, grad):

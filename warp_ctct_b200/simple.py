@@ -48,6 +48,27 @@ def log_matmul(lhs: T, rhs: T) -> T:
     return out
 
 
+def log_matmul_tc(f: T, g: T) -> T:
+    """den[b,i,j] = log sum_k exp(f[b,i,k] + g[b,j,k]) for contiguous float32 f (B,M,K), g (B,N,K):
+    the tensor-core path (tcgen05 GEMM on max-shifted exponentials, log/max epilogue) when the
+    shape allows it (K % 8 == 0, K >= 64), otherwise the exact kernel.  Same values as
+    ``log_matmul(f, g.transpose(1, 2))`` to float32 rounding."""
+    B, M, K = f.shape
+    N = g.size(1)
+    lib = _lib.lib()
+    nbytes = lib.ctct_b200_log_matmul_tc_workspace_bytes(B, M, N, K)
+    if nbytes == 0 or not (f.is_contiguous() and g.is_contiguous()):
+        return log_matmul(f, g.transpose(1, 2))
+    dev = f.device
+    den = torch.empty((B, M, N), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        ws = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
+        rc = lib.ctct_b200_log_matmul_tc(f.data_ptr(), g.data_ptr(), B, M, N, K, den.data_ptr(), ws.data_ptr(), nbytes,
+                                         _lib.stream_ptr(dev))
+    _lib.check(rc, "ctct_b200_log_matmul_tc")
+    return den
+
+
 def log_matmul_backward(grad_out: Optional[T], lhs: T, rhs: T, res: T, grad_masks):
     """(grad_lhs, grad_rhs) of ``log_matmul`` for any (signed) ``grad_out``
     (``_C.log_matmul_backward``, csrc/binding.cpp:247-324)."""
@@ -106,7 +127,7 @@ class FusedSimpleCTCTLoss(torch.autograd.Function):
         dev = f.device
         lib = _lib.lib()
         want_grad = track_f or track_g
-        den = log_matmul(f, g.transpose(1, 2)) if normalized else None
+        den = log_matmul_tc(f, g) if normalized else None
         costs = torch.empty((N,), dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             ws = _lib.workspace(N, Tm, U1, want_grad, dev)
