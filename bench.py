@@ -34,6 +34,11 @@ WORKLOADS = {
     "c3": (16, 512, 129, 1024, "f16", 2.0, (256, 512), (32, 128), False),
     "c5": (32, 400, 101, 1024, "f16", 2.0, (100, 400), (10, 100), True),
 }
+# ctct_simple_loss (log-add joiner): (B per GPU, T, U+1, V, lx range, ly range); f, g ~ N(0,1) fp32
+SIMPLE_WORKLOADS = {
+    "c4": (32, 500, 101, 4096, (250, 500), (25, 100)),
+    "c4s": (4, 500, 101, 4096, (250, 500), (25, 100)),   # small case of the same kernels for ncu captures
+}
 METRIC = "utterances/sec fwd+bwd"
 UNIT = "utt/s"
 
@@ -49,7 +54,11 @@ def workload_string(name, n_gpus):
 
 
 def global_lengths(name, n_gpus, seed=2000):
-    B, T, U1, V, dt, sigma, lxr, lyr, cap = WORKLOADS[name]
+    if name in SIMPLE_WORKLOADS:
+        B, T, U1, V, lxr, lyr = SIMPLE_WORKLOADS[name]
+        cap = False
+    else:
+        B, T, U1, V, dt, sigma, lxr, lyr, cap = WORKLOADS[name]
     rng = np.random.default_rng(seed)
     G = B * n_gpus
     lx = rng.integers(lxr[0], lxr[1] + 1, G).astype(np.int32)
@@ -61,13 +70,13 @@ def global_lengths(name, n_gpus, seed=2000):
     return lx, ly, ys
 
 
-def peaks():
+def peaks(key="hbm_gbs", fallback=6650.0):
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         with open(path) as fh:
-            return float(json.load(fh)["hbm_gbs"]), "measured"
+            return float(json.load(fh)[key]), "measured"
     except Exception:
-        return 6650.0, "fallback"
+        return fallback, "fallback"
 
 
 class ClockSampler(threading.Thread):
@@ -164,13 +173,10 @@ def run_reference(args):
 
 # --------------------------------------------------------------------------------------- B200 arm
 
-def run_b200(args):
+def setup_device(args):
+    """One process per GPU: picks the device, brings up NCCL under torchrun.  Returns (world, rank, local_rank, dev)."""
     import torch
     import torch.distributed as dist
-
-    import warp_ctct_b200 as W
-    from warp_ctct_b200 import _lib
-    from warp_ctct_b200.sharded import plan_shards, sharded_ctct_loss, shard_weights
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -196,6 +202,18 @@ def run_b200(args):
             sys.stdout.flush()
             os.dup2(saved, 1)
             os.close(saved)
+    return world, rank, local_rank, dev
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    import warp_ctct_b200 as W
+    from warp_ctct_b200 import _lib
+    from warp_ctct_b200.sharded import plan_shards, sharded_ctct_loss, shard_weights
+
+    world, rank, local_rank, dev = setup_device(args)
     lib = _lib.lib()
 
     B, T, U1, V, dt, sigma, lxr, lyr, cap = WORKLOADS[args.workload]
@@ -361,21 +379,230 @@ def run_b200(args):
     return 0
 
 
+# --------------------------------------------------------------------------------------- ctct_simple_loss (c4)
+
+def simple_inputs_host(name, seed=2000):
+    B, T, U1, V, lxr, lyr = SIMPLE_WORKLOADS[name]
+    rng = np.random.default_rng(seed)
+    f = rng.standard_normal((B, T, V), dtype=np.float32)
+    g = rng.standard_normal((B, U1, V), dtype=np.float32)
+    return f, g
+
+
+def simple_workload_string(name, n_gpus):
+    B, T, U1, V, lxr, lyr = SIMPLE_WORKLOADS[name]
+    return (f"{name}: ctct_simple_loss f32 fwd+bwd (normalized), B={B}/GPU (global {B * n_gpus}), T={T}, U+1={U1}, "
+            f"V={V}, f,g~N(0,1), lx~U{list(lxr)}, ly~U{list(lyr)}")
+
+
+def run_reference_simple(args):
+    """CPU arm for the log-add-joiner loss: the C restatement on all host threads, on a bounded
+    sample of the batch (the first utterances) so that a run ends within minutes."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0
+    import oracle
+    B, T, U1, V, lxr, lyr = SIMPLE_WORKLOADS[args.workload]
+    lx, ly, ys = global_lengths(args.workload, 1)
+    f, g = simple_inputs_host(args.workload)
+    nb = min(B, 4)
+    cores = oracle.max_threads()
+    go = np.full((nb,), 1.0 / B, np.float32)
+
+    def one():
+        return oracle.simple_loss(f[:nb], g[:nb], ys[:nb], lx[:nb], ly[:nb], True, go, nthreads=cores)
+
+    for _ in range(min(args.warmup, 1)):
+        one()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one()
+    dt_s = time.perf_counter() - t0
+    value = nb * args.steps / dt_s
+    sample = f"every step = the first {nb} of {B} utterances on {cores} OpenMP threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * dt_s / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": simple_workload_string(args.workload, 1)},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_b200_simple(args):
+    import torch
+    import torch.distributed as dist
+
+    from warp_ctct_b200 import _lib
+    from warp_ctct_b200.sharded import plan_shards, shard_weights, sharded_ctct_simple_loss
+
+    world, rank, local_rank, dev = setup_device(args)
+    lib = _lib.lib()
+    B, T, U1, V, lxr, lyr = SIMPLE_WORKLOADS[args.workload]
+    lx_g, ly_g, ys_g = global_lengths(args.workload, world)
+    plan = plan_shards(lx_g, ly_g, world)
+    mine = np.array(plan[rank])
+    lx, ly, ys = lx_g[mine], ly_g[mine], ys_g[mine]
+    assert len(mine) == B
+    G = B * world
+
+    f_np, g_np = simple_inputs_host(args.workload, 2000 + rank)
+    f_host = torch.from_numpy(f_np).pin_memory()
+    g_host = torch.from_numpy(g_np).pin_memory()
+    ys_h = torch.from_numpy(ys).pin_memory()
+    lx_h = torch.from_numpy(lx).pin_memory()
+    ly_h = torch.from_numpy(ly).pin_memory()
+    f = f_host.to(dev).requires_grad_(True)
+    g = g_host.to(dev).requires_grad_(True)
+    ys_t, lx_t, ly_t = ys_h.to(dev), lx_h.to(dev), ly_h.to(dev)
+
+    def step():
+        f.grad = None
+        g.grad = None
+        loss = sharded_ctct_simple_loss(f, g, ys_t, lx_t, ly_t, global_batch=G, reduction="mean")
+        loss.backward()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    cap_n = 3 * args.steps + 3
+    _lib.check(lib.ctct_b200_profile_enable(cap_n), "profile_enable")
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.start()
+    barrier()
+    ev0.record()
+    t_host = time.perf_counter()
+    for _ in range(args.steps):
+        loss = step()
+    host_us = 1e6 * (time.perf_counter() - t_host) / args.steps
+    ev1.record()
+    barrier()
+    clocks = sampler.finish() if sampler else None
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+
+    buf = np.zeros((cap_n, 4), np.float32)
+    kinds = np.zeros((cap_n,), np.int32)
+    n_rec = lib.ctct_b200_profile_read(buf.ctypes.data, kinds.ctypes.data, cap_n)
+    lib.ctct_b200_profile_disable()
+    rec = {k: buf[:n_rec][kinds[:n_rec] == k] for k in (3, 4, 5)}
+    k_ms = {
+        "exp_split": float(rec[3][:, 0].mean()), "logmm_tc": float(rec[3][:, 1].mean()),
+        "logmm_exact_fixup": float(rec[3][:, 2].mean()),
+        "compose": float(rec[4][:, 0].mean()), "lattice": float(rec[4][:, 1].mean()),
+        "fill_grad": float(rec[4][:, 2].mean()),
+        "denominator_backward": float(rec[5][:, 0].mean()), "label_patches": float(rec[5][:, 1].mean()),
+    }
+    value = G * args.steps / (ms_total * 1e-3)
+    tc_peak, tc_kind = peaks("bf16_tflops", 1590.0)
+    hbm_peak, hbm_kind = peaks()
+    flops = 2.0 * B * T * U1 * V                       # one multiply-add per (t, u, v): the contraction itself
+    tc_ach = flops / (k_ms["logmm_tc"] * 1e-3) / 1e12
+    roofline = {"kernel": "k_logmm_tc (tcgen05 GEMM of the max-shifted exponentials, log/max epilogue)",
+                "bound": "tensor", "achieved": tc_ach, "peak": tc_peak, "unit": "TFLOP/s", "frac": tc_ach / tc_peak,
+                "peak_source": f"of {tc_kind} (burst cuBLAS bf16)", "algorithmic_flops": flops,
+                "issued_flops": 3 * flops, "traffic": NCU_TRAFFIC_PER_LAUNCH.get(args.workload),
+                "note": "each product is issued as three bf16 MMAs (hi*hi, hi*lo, lo*hi) for float32-level accuracy; "
+                        "at these shapes the kernel is bound by its operand planes (HBM/L2), not the tensor pipe"}
+    plane_bytes = 2 * 2 * (B * T * V + B * U1 * V)      # bf16 hi+lo planes of both operands, read once
+    split_bytes = 4 * (B * T * V + B * U1 * V) + plane_bytes
+    bwd_bytes = 4 * (2 * B * T * V + 2 * B * U1 * V + B * T * U1 * 5)
+    kernels = {k: {"ms": v} for k, v in k_ms.items()}
+    kernels["exp_split"].update({"GB/s": split_bytes / (k_ms["exp_split"] * 1e-3) / 1e9,
+                                 "frac": split_bytes / (k_ms["exp_split"] * 1e-3) / 1e9 / hbm_peak})
+    kernels["logmm_tc"].update({"TFLOP/s": tc_ach, "operand_GB/s": plane_bytes / (k_ms["logmm_tc"] * 1e-3) / 1e9})
+    kernels["denominator_backward"].update({"GB/s": bwd_bytes / (k_ms["denominator_backward"] * 1e-3) / 1e9,
+                                            "frac": bwd_bytes / (k_ms["denominator_backward"] * 1e-3) / 1e9 / hbm_peak,
+                                            "hbm_peak_source": f"of {hbm_kind}"})
+    kernels["sum_ms"] = sum(k_ms.values())
+
+    # ---- end to end: f and g copied from pinned host memory each step, loss read back ----
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+
+    def e2e_step():
+        a = f_host.to(dev, non_blocking=True).requires_grad_(True)
+        b = g_host.to(dev, non_blocking=True).requires_grad_(True)
+        y, p, q = ys_h.to(dev, non_blocking=True), lx_h.to(dev, non_blocking=True), ly_h.to(dev, non_blocking=True)
+        out = sharded_ctct_simple_loss(a, b, y, p, q, global_batch=G, reduction="mean")
+        out.backward()
+        return float(out.item())
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    ev0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    ev1.record()
+    barrier()
+    ms_e = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms_e, op=dist.ReduceOp.MAX)
+    h2d = 4 * (f_host.numel() + g_host.numel() + ys_h.numel() + lx_h.numel() + ly_h.numel())
+    e2e = {"value": G * e2e_steps / (float(ms_e.item()) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(h2d * world),
+           "d2h_bytes_per_step": 4 * world, "steps": e2e_steps,
+           "note": "f and g copied from pinned host memory every step; gradients stay on the device, the loss is read back"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": simple_workload_string(args.workload, world),
+                   "l2": f"inputs larger than L2: f {4 * B * T * V / 1e6:.0f} MB, g {4 * B * U1 * V / 1e6:.0f} MB, "
+                         f"their gradients as much again, bf16 planes {plane_bytes / 1e6:.0f} MB (L2 is 126 MB)",
+                   "shard_weights": shard_weights(lx_g, ly_g, plan)},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": 10 * args.steps * world,
+        "roofline": roofline, "kernels": kernels, "host_enqueue_us_per_step": host_us,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle
+        cores = oracle.max_threads()
+        nb = min(B, 4)
+        go = np.full((nb,), 1.0 / B, np.float32)
+        t0 = time.perf_counter()
+        costs_cpu, _, _ = oracle.simple_loss(f_np[:nb], g_np[:nb], ys[:nb], lx[:nb], ly[:nb], True, go, nthreads=cores)
+        dt_s = time.perf_counter() - t0
+        with torch.no_grad():
+            from warp_ctct_b200 import ctct_simple_loss
+            costs_gpu = ctct_simple_loss(f[:nb], g[:nb], ys_t[:nb], lx_t[:nb], ly_t[:nb], reduction="none").cpu().numpy()
+        line["cpu_baseline"] = {"value": nb / dt_s, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"the first {nb} of {B} utterances, one pass, {cores} OpenMP threads; costs "
+                                          f"agree with the GPU to {float(np.abs(costs_cpu - costs_gpu).max() / np.abs(costs_cpu).max()):.1e} rel"}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(SIMPLE_WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps == 200 and "--steps" not in " ".join(sys.argv):
             args.steps, args.warmup = 10, 3
-        return run_reference(args)
-    return run_b200(args)
+        return run_reference_simple(args) if args.workload in SIMPLE_WORKLOADS else run_reference(args)
+    return run_b200_simple(args) if args.workload in SIMPLE_WORKLOADS else run_b200(args)
 
 
 if __name__ == "__main__":

@@ -258,6 +258,21 @@ int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const 
                               void *stream);
 
 /*
+ * The same gradients with the part through the denominator (log_matmul_backward,
+ * csrc/binding.cpp:247-324) computed as two tensor-core GEMMs,
+ *     grad_f = Ef * (P  Eg),   grad_g = Eg * (P^T Ef),   P = w * exp(mf + mg - den),
+ * on the bf16 planes of Ef = exp(f - max f), Eg = exp(g - max g) that ctct_b200_log_matmul_tc left
+ * in its workspace.  tc_workspace must be the buffer passed to ctct_b200_log_matmul_tc for the same
+ * f, g (B = N, M = T, N = U1, K = V), not written since; den must be its result.  If that call had
+ * to fall back to the exact kernel (a flag in the workspace says so) this one does too, inside the
+ * same launches.  den must not be NULL; f, g, grad_f, grad_g 16-byte aligned.
+ */
+int ctct_b200_simple_backward_tc(const float *grads3, const float *grad_out, const float *f, const float *g,
+                                 const float *den, const int32_t *ys, const int32_t *lx, const int32_t *ly,
+                                 int64_t N, int64_t T, int64_t U1, int64_t V, float *grad_f, float *grad_g,
+                                 void *tc_workspace, size_t tc_workspace_bytes, void *stream);
+
+/*
  * Optional per-kernel timing for benchmarks (no counterpart in the reference).  While
  * enabled, every ctct_b200_loss_forward records CUDA events on its stream before the gather,
  * after the gather, after the lattice and after the occupancy-gradient kernel, and every
@@ -265,8 +280,11 @@ int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const 
  * Events are created once by _enable (room for max_calls calls, shared by all host threads) and
  * destroyed by _disable; nothing is recorded when profiling is off.
  *   ctct_b200_profile_read: waits for the recorded events, writes for call i
- *     kind[i] (0 forward, 1 backward, 2 zero fill) and ms[4*i .. 4*i+2] = {gather, lattice,
- *     fill_grad} or {dense gradient / patch / zero fill, 0, 0}; returns the number of calls recorded (<= capacity) or a
+ *     kind[i] (0 forward, 1 backward, 2 zero fill, 3 log_matmul_tc, 4 simple_forward,
+ *     5 simple_backward) and ms[4*i .. 4*i+2] = {gather, lattice, fill_grad} (kind 0),
+ *     {dense gradient / patch / zero fill, 0, 0} (kinds 1, 2), {exp + bf16 split of both operands,
+ *     tensor-core kernel, exact fix-up} (kind 3), {compose, lattice, fill_grad} (kind 4),
+ *     {gradient through the denominator, label patches, 0} (kind 5); returns the number of calls recorded (<= capacity) or a
  *     negative error code, and rewinds the recorder.
  */
 int ctct_b200_profile_enable(int max_calls);

@@ -151,6 +151,10 @@ def test_logmmexp_autograd_matches_logsumexp(W):
     ((3, 40, 17, 130), 3, dict(lx_range=(20, 40), ly_range=(4, 16))),
     ((2, 30, 34, 67), 4, dict(lx_range=(30, 30), ly_range=(20, 28))),
     ((2, 60, 21, 4096), 5, dict(lx_range=(30, 60), ly_range=(5, 20))),   # vocabulary of the benchmark config
+    # shapes the tensor-core path takes (V % 8 == 0, V >= 64): more than one tile / chunk / k-block each way
+    ((3, 140, 70, 256), 6, dict(lx_range=(70, 140), ly_range=(30, 69))),
+    ((2, 33, 131, 64), 7, dict(lx_range=(33, 33), ly_range=(10, 30))),
+    ((2, 260, 9, 72), 8, dict(lx_range=(100, 260), ly_range=(3, 8), repeat_prob=0.3)),
 ])
 @pytest.mark.parametrize("normalized", [True, False])
 def test_simple_loss_costs_and_gradients(W, shape, seed, kw, normalized):
@@ -166,15 +170,33 @@ def test_simple_loss_costs_and_gradients(W, shape, seed, kw, normalized):
     assert np.isfinite(c_ref).all()
     np.testing.assert_allclose(costs.detach().cpu().numpy(), c_ref, rtol=1e-5)
     np.testing.assert_allclose(costs.detach().cpu().numpy(), c32, rtol=1e-5)
-    # the float32 restatement against its own float64 evaluation shows the noise floor of the
-    # reference arithmetic; the kernels are compared with the float64 one
-    assert np.abs(gf32 - gf_ref).max() < 1e-3 and np.abs(gg32 - gg_ref).max() < 1e-3
+    # the float32 restatement differs from its own float64 evaluation by up to 1e-4 * (frames summed)
+    # in grad_g (the noise floor of the reference arithmetic); the kernels are held to the float64 one
+    assert np.abs(gf32 - gf_ref).max() < 5e-3 and np.abs(gg32 - gg_ref).max() < 2e-4 * T
     # entries of grad_f / grad_g are sums of up to T*(U+1) occupancies (|value| up to ~T), so the
     # 1e-4 absolute bound on a single occupancy becomes 1e-4 + 2e-5 relative on the sums
     np.testing.assert_allclose(f_t.grad.cpu().numpy(), gf_ref, atol=1e-4, rtol=2e-5)
     np.testing.assert_allclose(g_t.grad.cpu().numpy(), gg_ref, atol=1e-4, rtol=2e-5)
     for n in range(N):   # nothing flows into padding frames / contexts
         assert not f_t.grad[n, lx[n]:].any().item() and not g_t.grad[n, ly[n] + 1:].any().item()
+
+
+def test_simple_loss_wide_range_falls_back_to_exact_kernels(W):
+    """A frame and a context whose maxima sit at different vocabulary entries, 300 nats above the
+    rest: the max-shifted sums underflow, and both the denominator and its gradient must come from
+    the exact kernels inside the same calls."""
+    N, T, U1, V = 2, 24, 7, 128
+    f, g, ys, lx, ly = _case(N, T, U1, V, 21, (16, 24), (2, 6))
+    f[0, 5, 3] += 300.0
+    g[0, 2, 90] += 300.0
+    f_t, g_t = [t.requires_grad_(True) for t in _dev(f, g)]
+    ys_t, lx_t, ly_t = _dev(ys, lx, ly)
+    costs = W.ctct_simple_loss(f_t, g_t, ys_t, lx_t, ly_t, reduction="none")
+    costs.sum().backward()
+    c_ref, gf_ref, gg_ref = oracle.simple_loss(f, g, ys, lx, ly, True, dtype=np.float64)
+    np.testing.assert_allclose(costs.detach().cpu().numpy(), c_ref, rtol=1e-5)
+    np.testing.assert_allclose(f_t.grad.cpu().numpy(), gf_ref, atol=1e-4, rtol=2e-5)
+    np.testing.assert_allclose(g_t.grad.cpu().numpy(), gg_ref, atol=1e-4, rtol=2e-5)
 
 
 def test_simple_loss_equals_standard_loss_on_the_joint(W):

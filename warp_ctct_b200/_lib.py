@@ -47,6 +47,8 @@ SIGNATURES = {
     "ctct_b200_log_matmul_backward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
     "ctct_b200_simple_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
     "ctct_b200_simple_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
+    "ctct_b200_simple_backward_tc": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp,
+                                            _sz, _vp]),
     "ctct_b200_profile_enable": (_int, [_int]),
     "ctct_b200_profile_read": (_int, [_vp, _vp, _int]),
     "ctct_b200_profile_disable": (_int, []),

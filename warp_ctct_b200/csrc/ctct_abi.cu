@@ -11,6 +11,7 @@
 #include "lattice.cuh"
 #include "simple.cuh"
 #include "logmm_tc.cuh"
+#include "logmm_bwd_tc.cuh"
 
 using namespace ctct;
 
@@ -334,12 +335,12 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // bf16 plane (B, rows, K), K contiguous -> 3-D tensor map with a 64 x 128 x 1 box, 128-byte swizzle
-bool make_plane_map(CUtensorMap *map, const void *ptr, int64_t B, int64_t rows, int64_t K) {
+bool make_plane_map(CUtensorMap *map, const void *ptr, int64_t B, int64_t rows, int64_t K, int box_rows = TC_BM) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     const cuuint64_t gdim[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)B};
     const cuuint64_t gstride[2] = {(cuuint64_t)K * 2, (cuuint64_t)rows * K * 2};
-    const cuuint32_t box[3] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM, 1};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};  // 64 bf16 = one 128-byte swizzle row
     const cuuint32_t estr[3] = {1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), gdim, gstride, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -347,7 +348,8 @@ bool make_plane_map(CUtensorMap *map, const void *ptr, int64_t B, int64_t rows, 
 }
 
 struct TcLayout {
-    size_t ah, al, bh, bl, mf, mg, flags, total;
+    size_t ah, al, bh, bl, mf, mg, flags, ph, pl, total;
+    int64_t Np;  // N rounded up to 8 columns (16-byte rows of the weight planes)
 };
 TcLayout tc_layout(int64_t B, int64_t M, int64_t N, int64_t K) {
     TcLayout l;
@@ -359,6 +361,10 @@ TcLayout tc_layout(int64_t B, int64_t M, int64_t N, int64_t K) {
     l.mf = o; o = align256(o + (size_t)B * M * 4);
     l.mg = o; o = align256(o + (size_t)B * N * 4);
     l.flags = o; o = align256(o + 16);
+    // backward pass: weight planes P (B, M, Np), bf16 hi and lo
+    l.Np = (N + 7) / 8 * 8;
+    l.ph = o; o = align256(o + (size_t)B * M * l.Np * 2);
+    l.pl = o; o = align256(o + (size_t)B * M * l.Np * 2);
     l.total = o;
     return l;
 }
@@ -711,12 +717,15 @@ int ctct_b200_log_matmul_tc(const float *f, const float *g, int64_t B, int64_t M
         return CTCT_ERR_LAUNCH;
     }
     if (cudaMemsetAsync(flags, 0, 16, st) != cudaSuccess) return check_launch("log_matmul_tc flags");
+    cudaEvent_t *slot = prof_slot(3);
+    prof_mark(slot, 0, st);
     k_exp_split<<<static_cast<unsigned>(B * M), 256, 0, st>>>(f, (int)K, ah, al, mf);
     int rc = check_launch("exp_split f");
     if (rc) return rc;
     k_exp_split<<<static_cast<unsigned>(B * N), 256, 0, st>>>(g, (int)K, bh, bl, mg);
     rc = check_launch("exp_split g");
     if (rc) return rc;
+    prof_mark(slot, 1, st);
     static std::once_flag attr_once;
     std::call_once(attr_once, [] {
         cudaFuncSetAttribute(k_logmm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
@@ -733,8 +742,11 @@ int ctct_b200_log_matmul_tc(const float *f, const float *g, int64_t B, int64_t M
     k_logmm_tc<<<grid, 128, TC_SMEM_BYTES, st>>>(m_ah, m_al, m_bh, m_bl, a);
     rc = check_launch("log_matmul_tc");
     if (rc) return rc;
+    prof_mark(slot, 2, st);
     // exact kernel, a no-op unless a wait ran out or a shifted sum underflowed
-    return launch_logmm(f, M * K, K, 1, g, N * K, 1, K, B, M, K, N, den, st, flags);
+    rc = launch_logmm(f, M * K, K, 1, g, N * K, 1, K, B, M, K, N, den, st, flags);
+    prof_mark(slot, 3, st);
+    return rc;
 }
 
 int ctct_b200_log_matmul_backward(const float *grad_out, const float *lhs, const float *rhsT, const float *res,
@@ -780,6 +792,8 @@ int ctct_b200_simple_forward(const float *f, const float *g, const float *den, c
     c.U1 = (int)U1;
     c.V = (int)V;
     c.total = N * T * U1 * 4;
+    cudaEvent_t *slot = prof_slot(4);
+    prof_mark(slot, 0, st);
     if (c.total > 0) {
         const int64_t want = (c.total + 255) / 256;
         const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
@@ -787,15 +801,91 @@ int ctct_b200_simple_forward(const float *f, const float *g, const float *den, c
         int rc = check_launch("simple_compose");
         if (rc) return rc;
     }
+    prof_mark(slot, 1, st);
     int rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st);
     if (rc) return rc;
+    prof_mark(slot, 2, st);
     if (want_grad) rc = launch_fill_grad(w, ws, ys, lx, ly, grads3, 0, N, T, U1, st);
+    prof_mark(slot, 3, st);
     return rc;
 }
 
-int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const float *f, const float *g,
-                              const float *den, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
-                              int64_t T, int64_t U1, int64_t V, float *grad_f, float *grad_g, void *stream) {
+// tensor-core gradient through the denominator; planes, maxima and flags are those the forward
+// pass (ctct_b200_log_matmul_tc) left in tc_ws
+static int den_backward_tc(const float4 *g4, const float *grad_out, const float *f, const float *g, const float *den,
+                           const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
+                           float *grad_f, float *grad_g, char *ws, const TcLayout &l, cudaStream_t st) {
+    auto *ah = reinterpret_cast<__nv_bfloat16 *>(ws + l.ah), *al = reinterpret_cast<__nv_bfloat16 *>(ws + l.al);
+    auto *bh = reinterpret_cast<__nv_bfloat16 *>(ws + l.bh), *bl = reinterpret_cast<__nv_bfloat16 *>(ws + l.bl);
+    auto *ph = reinterpret_cast<__nv_bfloat16 *>(ws + l.ph), *pl = reinterpret_cast<__nv_bfloat16 *>(ws + l.pl);
+    float *mf = reinterpret_cast<float *>(ws + l.mf), *mg = reinterpret_cast<float *>(ws + l.mg);
+    int *flags = reinterpret_cast<int *>(ws + l.flags);
+    DenWeightArgs w;
+    w.grads3 = g4;
+    w.scale = grad_out;
+    w.den = den;
+    w.mf = mf;
+    w.mg = mg;
+    w.lx = lx;
+    w.ly = ly;
+    w.ph = ph;
+    w.pl = pl;
+    w.T = (int)T;
+    w.U1 = (int)U1;
+    w.U1p = (int)l.Np;
+    w.flags = flags;
+    k_den_weights<<<static_cast<unsigned>(N * T), 128, 0, st>>>(w);
+    int rc = check_launch("den_weights");
+    if (rc) return rc;
+    static std::once_flag attr_once;
+    std::call_once(attr_once, [] {
+        cudaFuncSetAttribute(k_logmm_bwd_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BW_SMEM_BYTES);
+        cudaFuncSetAttribute(k_logmm_bwd_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BW_SMEM_BYTES);
+    });
+    CUtensorMap m_pk_h, m_pk_l, m_pm_h, m_pm_l, m_f_h, m_f_l, m_g_h, m_g_l;
+    if (!make_plane_map(&m_pk_h, ph, N, T, l.Np, BW_BM) || !make_plane_map(&m_pk_l, pl, N, T, l.Np, BW_BM) ||
+        !make_plane_map(&m_pm_h, ph, N, T, l.Np, BW_BK) || !make_plane_map(&m_pm_l, pl, N, T, l.Np, BW_BK) ||
+        !make_plane_map(&m_f_h, ah, N, T, V, BW_BK) || !make_plane_map(&m_f_l, al, N, T, V, BW_BK) ||
+        !make_plane_map(&m_g_h, bh, N, U1, V, BW_BK) || !make_plane_map(&m_g_l, bl, N, U1, V, BW_BK)) {
+        snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "cuTensorMapEncodeTiled failed");
+        return CTCT_ERR_LAUNCH;
+    }
+    const unsigned vt = (unsigned)((V + BW_BN - 1) / BW_BN);
+    if (grad_f) {  // grad_f[t,v] = Ef[t,v] * sum_u P[t,u] Eg[u,v]
+        LogmmBwdTcArgs a;
+        a.src = f;
+        a.mx = mf;
+        a.out = grad_f;
+        a.M = (int)T;
+        a.N = (int)V;
+        a.K = (int)U1;
+        a.flags = flags;
+        dim3 grid((unsigned)((T + BW_BM - 1) / BW_BM), vt, (unsigned)N);
+        k_logmm_bwd_tc<false><<<grid, 128, BW_SMEM_BYTES, st>>>(m_pk_h, m_pk_l, m_g_h, m_g_l, a);
+        rc = check_launch("logmm_bwd_tc grad_f");
+        if (rc) return rc;
+    }
+    if (grad_g) {  // grad_g[u,v] = Eg[u,v] * sum_t P[t,u] Ef[t,v]
+        LogmmBwdTcArgs a;
+        a.src = g;
+        a.mx = mg;
+        a.out = grad_g;
+        a.M = (int)U1;
+        a.N = (int)V;
+        a.K = (int)T;
+        a.flags = flags;
+        dim3 grid((unsigned)((U1 + BW_BM - 1) / BW_BM), vt, (unsigned)N);
+        k_logmm_bwd_tc<true><<<grid, 128, BW_SMEM_BYTES, st>>>(m_pm_h, m_pm_l, m_f_h, m_f_l, a);
+        rc = check_launch("logmm_bwd_tc grad_g");
+        if (rc) return rc;
+    }
+    return CTCT_OK;
+}
+
+static int simple_backward_impl(const float *grads3, const float *grad_out, const float *f, const float *g,
+                                const float *den, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
+                                int64_t T, int64_t U1, int64_t V, float *grad_f, float *grad_g, void *tc_ws,
+                                size_t tc_ws_bytes, void *stream) {
     if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
     if (N == 0) return CTCT_OK;
     if (!grads3 || !grad_out || !lx || !ly || (U1 > 1 && !ys) || (den && (!f || !g))) return CTCT_ERR_ARG;
@@ -803,7 +893,24 @@ int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const 
     if (reinterpret_cast<uintptr_t>(grads3) % 16) return CTCT_ERR_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const float4 *g4 = reinterpret_cast<const float4 *>(grads3);
+    cudaEvent_t *slot = prof_slot(5);
+    prof_mark(slot, 0, st);
     if (den) {
+        const int *run_flags = nullptr;
+        if (tc_ws) {
+            if (!tc_shape_ok(N, T, U1, V)) return CTCT_ERR_UNSUPPORTED;
+            const TcLayout l = tc_layout(N, T, U1, V);
+            if (tc_ws_bytes < l.total || reinterpret_cast<uintptr_t>(tc_ws) % 256) return CTCT_ERR_WORKSPACE;
+            if (reinterpret_cast<uintptr_t>(f) % 16 || reinterpret_cast<uintptr_t>(g) % 16 ||
+                (grad_f && reinterpret_cast<uintptr_t>(grad_f) % 16) || (grad_g && reinterpret_cast<uintptr_t>(grad_g) % 16))
+                return CTCT_ERR_ARG;
+            int rc = den_backward_tc(g4, grad_out, f, g, den, lx, ly, N, T, U1, V, grad_f, grad_g,
+                                     static_cast<char *>(tc_ws), l, st);
+            if (rc) return rc;
+            run_flags = reinterpret_cast<const int *>(static_cast<char *>(tc_ws) + l.flags);
+        }
+        // exact kernel: the whole job without a tensor-core workspace, otherwise a no-op unless a
+        // flag in that workspace says the tensor-core result cannot be used
         LogmmBwdArgs a = {};
         a.lhs = f;
         a.rhsT = g;
@@ -817,12 +924,14 @@ int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const 
         a.M = (int)T;
         a.Nc = (int)U1;
         a.K = (int)V;
+        a.run_flags = run_flags;
         int rc = launch_logmm_bwd(a, N, st);
         if (rc) return rc;
     } else {
         if (grad_f && cudaMemsetAsync(grad_f, 0, sizeof(float) * N * T * V, st) != cudaSuccess) return check_launch("memset grad_f");
         if (grad_g && cudaMemsetAsync(grad_g, 0, sizeof(float) * N * U1 * V, st) != cudaSuccess) return check_launch("memset grad_g");
     }
+    prof_mark(slot, 1, st);
     PatchArgs p;
     p.grads3 = g4;
     p.scale = grad_out;
@@ -846,7 +955,23 @@ int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const 
         int rc = check_launch("simple_patch_g");
         if (rc) return rc;
     }
+    prof_mark(slot, 2, st);
     return CTCT_OK;
+}
+
+int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const float *f, const float *g,
+                              const float *den, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
+                              int64_t T, int64_t U1, int64_t V, float *grad_f, float *grad_g, void *stream) {
+    return simple_backward_impl(grads3, grad_out, f, g, den, ys, lx, ly, N, T, U1, V, grad_f, grad_g, nullptr, 0, stream);
+}
+
+int ctct_b200_simple_backward_tc(const float *grads3, const float *grad_out, const float *f, const float *g,
+                                 const float *den, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
+                                 int64_t T, int64_t U1, int64_t V, float *grad_f, float *grad_g, void *tc_workspace,
+                                 size_t tc_workspace_bytes, void *stream) {
+    if (!tc_workspace || !den) return CTCT_ERR_ARG;
+    return simple_backward_impl(grads3, grad_out, f, g, den, ys, lx, ly, N, T, U1, V, grad_f, grad_g, tc_workspace,
+                                tc_workspace_bytes, stream);
 }
 
 static int profile_disable_locked() {
@@ -889,7 +1014,8 @@ int ctct_b200_profile_read(float *ms, int *kind, int capacity) {
     const int n = g_prof.used < capacity ? g_prof.used : capacity;
     for (int i = 0; i < n; ++i) {
         cudaEvent_t *e = g_prof.ev + 4 * i;
-        const int pairs = g_prof.kind[i] == 0 ? 3 : 1;  // forward: three intervals; others: one
+        const int k_ = g_prof.kind[i];
+        const int pairs = (k_ == 0 || k_ == 3 || k_ == 4) ? 3 : (k_ == 5 ? 2 : 1);  // intervals recorded per kind
         if (cudaEventSynchronize(e[pairs]) != cudaSuccess) return check_launch("profile sync");
         kind[i] = g_prof.kind[i];
         for (int k = 0; k < 3; ++k) {

@@ -122,6 +122,18 @@ __device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;
     return d;
 }
+// MN-major operand tile (the M or N index is the contiguous one), 128-byte swizzle: rows are k,
+// 128 bytes (64 elements of M/N) each; groups of 8 k-rows are 1024 bytes apart (SBO = 64) and
+// successive 64-element chunks of M/N are lbo_bytes apart
+__device__ __forceinline__ uint64_t umma_desc_mn(unsigned smem_addr, unsigned lbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fff);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= static_cast<uint64_t>(64) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
 __device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -217,7 +229,6 @@ __global__ void __launch_bounds__(128) k_logmm_tc(const __grid_constant__ CUtens
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const unsigned st = tiles + s * TC_STAGE_BYTES;
-#pragma unroll
             // The tensor core truncates when it adds into the fp32 accumulator, a bias that grows
             // with the number of accumulation steps (3e-5 relative after 768 steps).  So the main
             // products hi*hi go round-robin into three accumulators (a third of the steps each)

@@ -142,6 +142,7 @@ struct LogmmBwdArgs {
     float *grad_lhs;        // (B,M,K) or nullptr
     float *grad_rhsT;       // (B,Nc,K) or nullptr
     int M, Nc, K;
+    const int *run_flags;   // optional {a, b}: run only if a or b is non-zero (fallback after the tensor-core kernels)
 };
 
 // One thread per k (vocabulary entry), VT threads per block; the block walks all (i,j) of one
@@ -150,6 +151,7 @@ struct LogmmBwdArgs {
 template <int VT>
 __global__ void __launch_bounds__(VT) k_logmm_bwd_exact(const LogmmBwdArgs a) {
     extern __shared__ float sm[];
+    if (a.run_flags != nullptr && a.run_flags[0] == 0 && a.run_flags[1] == 0) return;
     const int b = blockIdx.y;
     const int k = blockIdx.x * VT + threadIdx.x;
     const bool kin = k < a.K;

@@ -103,3 +103,27 @@ def sharded_ctct_loss(log_probs: torch.Tensor, labels: torch.Tensor, frames_leng
     costs = FusedCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
                                 enable_grad)
     return reduce_costs(costs, frames_lengths, global_batch, reduction, average_frames, group)
+
+
+def sharded_ctct_simple_loss(f: torch.Tensor, g: torch.Tensor, labels: torch.Tensor, frames_lengths: torch.Tensor,
+                             labels_lengths: torch.Tensor, global_batch: Optional[int] = None,
+                             reduction: Optional[str] = "mean", average_frames: bool = False,
+                             normalized: bool = True, group=None) -> torch.Tensor:
+    """``ctct_simple_loss`` (log-add joiner, warp_ctct/__init__.py:150-236) on this rank's shard of a
+    batch split across the process group; reductions as in ``sharded_ctct_loss``."""
+    from .simple import FusedSimpleCTCTLoss
+
+    assert reduction is None or reduction in ("none", "mean", "sum")
+    assert f.dim() == 3 and g.dim() == 3 and labels.dim() == 2
+    assert g.size(1) == labels.size(1) + 1
+    assert f.size(0) == g.size(0) == labels.size(0) == frames_lengths.size(0) == labels_lengths.size(0)
+    _require_cuda(f=f, g=g, ys=labels, lx=frames_lengths, ly=labels_lengths)
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    if global_batch is None:
+        global_batch = f.size(0) * world
+    track_f = f.requires_grad and torch.is_grad_enabled()
+    track_g = g.requires_grad and torch.is_grad_enabled()
+    costs = FusedSimpleCTCTLoss.apply(f.float().contiguous(), g.float().contiguous(), _as_int(labels),
+                                      _as_int(frames_lengths), _as_int(labels_lengths), bool(normalized),
+                                      track_f, track_g)
+    return reduce_costs(costs, frames_lengths, global_batch, reduction, bool(average_frames), group)

@@ -48,17 +48,20 @@ def log_matmul(lhs: T, rhs: T) -> T:
     return out
 
 
-def log_matmul_tc(f: T, g: T) -> T:
+def log_matmul_tc(f: T, g: T, keep_workspace: bool = False):
     """den[b,i,j] = log sum_k exp(f[b,i,k] + g[b,j,k]) for contiguous float32 f (B,M,K), g (B,N,K):
     the tensor-core path (tcgen05 GEMM on max-shifted exponentials, log/max epilogue) when the
     shape allows it (K % 8 == 0, K >= 64), otherwise the exact kernel.  Same values as
-    ``log_matmul(f, g.transpose(1, 2))`` to float32 rounding."""
+    ``log_matmul(f, g.transpose(1, 2))`` to float32 rounding.  With ``keep_workspace`` returns
+    (den, workspace): the workspace (None on the exact path) holds the operand planes that the
+    tensor-core backward pass of the simple loss reuses."""
     B, M, K = f.shape
     N = g.size(1)
     lib = _lib.lib()
     nbytes = lib.ctct_b200_log_matmul_tc_workspace_bytes(B, M, N, K)
-    if nbytes == 0 or not (f.is_contiguous() and g.is_contiguous()):
-        return log_matmul(f, g.transpose(1, 2))
+    if nbytes == 0 or not (f.is_contiguous() and g.is_contiguous()) or f.data_ptr() % 16 or g.data_ptr() % 16:
+        den = log_matmul(f, g.transpose(1, 2))
+        return (den, None) if keep_workspace else den
     dev = f.device
     den = torch.empty((B, M, N), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
@@ -66,7 +69,7 @@ def log_matmul_tc(f: T, g: T) -> T:
         rc = lib.ctct_b200_log_matmul_tc(f.data_ptr(), g.data_ptr(), B, M, N, K, den.data_ptr(), ws.data_ptr(), nbytes,
                                          _lib.stream_ptr(dev))
     _lib.check(rc, "ctct_b200_log_matmul_tc")
-    return den
+    return (den, ws) if keep_workspace else den
 
 
 def log_matmul_backward(grad_out: Optional[T], lhs: T, rhs: T, res: T, grad_masks):
@@ -127,7 +130,9 @@ class FusedSimpleCTCTLoss(torch.autograd.Function):
         dev = f.device
         lib = _lib.lib()
         want_grad = track_f or track_g
-        den = log_matmul_tc(f, g) if normalized else None
+        den, tc_ws = (log_matmul_tc(f, g, keep_workspace=True) if normalized else (None, None))
+        if not want_grad:
+            tc_ws = None
         costs = torch.empty((N,), dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             ws = _lib.workspace(N, Tm, U1, want_grad, dev)
@@ -140,23 +145,31 @@ class FusedSimpleCTCTLoss(torch.autograd.Function):
                 _lib.stream_ptr(dev))
         _lib.check(rc, "ctct_b200_simple_forward")
         if want_grad:
-            ctx.save_for_backward(grads3, f, g, den if den is not None else f.new_empty(0), labels, lx, ly)
+            ctx.save_for_backward(grads3, f, g, den if den is not None else f.new_empty(0), labels, lx, ly,
+                                  tc_ws if tc_ws is not None else f.new_empty(0))
             ctx.meta = (N, Tm, U1, V, normalized, track_f, track_g)
         return costs
 
     @staticmethod
     def backward(ctx, grad_outputs: T):
-        grads3, f, g, den, labels, lx, ly = ctx.saved_tensors
+        grads3, f, g, den, labels, lx, ly, tc_ws = ctx.saved_tensors
         N, Tm, U1, V, normalized, track_f, track_g = ctx.meta
         dev = f.device
         go = grad_outputs.to(torch.float32).contiguous()
         grad_f = torch.empty((N, Tm, V), dtype=torch.float32, device=dev) if track_f else None
         grad_g = torch.empty((N, U1, V), dtype=torch.float32, device=dev) if track_g else None
         with torch.cuda.device(dev):
-            rc = _lib.lib().ctct_b200_simple_backward(
-                _lib.ptr(grads3), _lib.ptr(go), _lib.ptr(f), _lib.ptr(g), _lib.ptr(den) if normalized else None,
-                _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly), N, Tm, U1, V, _lib.ptr(grad_f), _lib.ptr(grad_g),
-                _lib.stream_ptr(dev))
+            if normalized and tc_ws.numel() > 0:
+                # gradient through the denominator as tensor-core GEMMs on the forward pass's planes
+                rc = _lib.lib().ctct_b200_simple_backward_tc(
+                    _lib.ptr(grads3), _lib.ptr(go), _lib.ptr(f), _lib.ptr(g), _lib.ptr(den),
+                    _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly), N, Tm, U1, V, _lib.ptr(grad_f), _lib.ptr(grad_g),
+                    _lib.ptr(tc_ws), tc_ws.numel(), _lib.stream_ptr(dev))
+            else:
+                rc = _lib.lib().ctct_b200_simple_backward(
+                    _lib.ptr(grads3), _lib.ptr(go), _lib.ptr(f), _lib.ptr(g), _lib.ptr(den) if normalized else None,
+                    _lib.ptr(labels), _lib.ptr(lx), _lib.ptr(ly), N, Tm, U1, V, _lib.ptr(grad_f), _lib.ptr(grad_g),
+                    _lib.stream_ptr(dev))
         _lib.check(rc, "ctct_b200_simple_backward")
         return grad_f, grad_g, None, None, None, None, None, None
 
