@@ -37,7 +37,7 @@ WORKLOADS = {
 # ctct_simple_loss (log-add joiner): (B per GPU, T, U+1, V, lx range, ly range); f, g ~ N(0,1) fp32
 SIMPLE_WORKLOADS = {
     "c4": (32, 500, 101, 4096, (250, 500), (25, 100)),
-    "c4s": (4, 500, 101, 4096, (250, 500), (25, 100)),   # small case of the same kernels for ncu captures
+    "c4s": (16, 500, 101, 4096, (250, 500), (25, 100)),   # small case of the same kernels for ncu captures
 }
 METRIC = "utterances/sec fwd+bwd"
 UNIT = "utt/s"
@@ -503,7 +503,8 @@ def run_b200_simple(args):
         "logmm_exact_fixup": float(rec[3][:, 2].mean()),
         "compose": float(rec[4][:, 0].mean()), "lattice": float(rec[4][:, 1].mean()),
         "fill_grad": float(rec[4][:, 2].mean()),
-        "denominator_backward": float(rec[5][:, 0].mean()), "label_patches": float(rec[5][:, 1].mean()),
+        "den_backward_grad_f": float(rec[5][:, 0].mean()), "den_backward_grad_g": float(rec[5][:, 1].mean()),
+        "label_patches": float(rec[5][:, 2].mean()),
     }
     value = G * args.steps / (ms_total * 1e-3)
     tc_peak, tc_kind = peaks("bf16_tflops", 1590.0)
@@ -518,14 +519,15 @@ def run_b200_simple(args):
                         "at these shapes the kernel is bound by its operand planes (HBM/L2), not the tensor pipe"}
     plane_bytes = 2 * 2 * (B * T * V + B * U1 * V)      # bf16 hi+lo planes of both operands, read once
     split_bytes = 4 * (B * T * V + B * U1 * V) + plane_bytes
-    bwd_bytes = 4 * (2 * B * T * V + 2 * B * U1 * V + B * T * U1 * 5)
+    gf_bytes = 4 * (2 * B * T * V + B * T * U1 * 5) + 4 * B * U1 * V     # f read, grad_f written, weights, Eg planes
+    gg_bytes = 4 * (2 * B * U1 * V) + 4 * B * T * V                      # g read, grad_g written, Ef planes
     kernels = {k: {"ms": v} for k, v in k_ms.items()}
     kernels["exp_split"].update({"GB/s": split_bytes / (k_ms["exp_split"] * 1e-3) / 1e9,
                                  "frac": split_bytes / (k_ms["exp_split"] * 1e-3) / 1e9 / hbm_peak})
     kernels["logmm_tc"].update({"TFLOP/s": tc_ach, "operand_GB/s": plane_bytes / (k_ms["logmm_tc"] * 1e-3) / 1e9})
-    kernels["denominator_backward"].update({"GB/s": bwd_bytes / (k_ms["denominator_backward"] * 1e-3) / 1e9,
-                                            "frac": bwd_bytes / (k_ms["denominator_backward"] * 1e-3) / 1e9 / hbm_peak,
-                                            "hbm_peak_source": f"of {hbm_kind}"})
+    for key, nbytes in (("den_backward_grad_f", gf_bytes), ("den_backward_grad_g", gg_bytes)):
+        kernels[key].update({"GB/s": nbytes / (k_ms[key] * 1e-3) / 1e9, "frac": nbytes / (k_ms[key] * 1e-3) / 1e9 / hbm_peak,
+                             "hbm_peak_source": f"of {hbm_kind}"})
     kernels["sum_ms"] = sum(k_ms.values())
 
     # ---- end to end: f and g copied from pinned host memory each step, loss read back ----

@@ -284,7 +284,8 @@ int ctct_b200_simple_backward_tc(const float *grads3, const float *grad_out, con
  *     5 simple_backward) and ms[4*i .. 4*i+2] = {gather, lattice, fill_grad} (kind 0),
  *     {dense gradient / patch / zero fill, 0, 0} (kinds 1, 2), {exp + bf16 split of both operands,
  *     tensor-core kernel, exact fix-up} (kind 3), {compose, lattice, fill_grad} (kind 4),
- *     {gradient through the denominator, label patches, 0} (kind 5); returns the number of calls recorded (<= capacity) or a
+ *     {denominator weights + grad_f GEMM (or the exact kernel), grad_g GEMM + exact fix-up, label
+ *     patches} (kind 5); returns the number of calls recorded (<= capacity) or a
  *     negative error code, and rewinds the recorder.
  */
 int ctct_b200_profile_enable(int max_calls);

@@ -343,7 +343,20 @@ bool make_plane_map(CUtensorMap *map, const void *ptr, int64_t B, int64_t rows, 
     const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};  // 64 bf16 = one 128-byte swizzle row
     const cuuint32_t estr[3] = {1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), gdim, gstride, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// fp32 tensor (B, rows, N), N contiguous -> 3-D tensor map with a 32 x 128 x 1 box, 128-byte swizzle
+bool make_f32_tile_map(CUtensorMap *map, const void *ptr, int64_t B, int64_t rows, int64_t N) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[3] = {(cuuint64_t)N, (cuuint64_t)rows, (cuuint64_t)B};
+    const cuuint64_t gstride[2] = {(cuuint64_t)N * 4, (cuuint64_t)rows * N * 4};
+    const cuuint32_t box[3] = {32, (cuuint32_t)BW_BM, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(ptr), gdim, gstride, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -812,9 +825,13 @@ int ctct_b200_simple_forward(const float *f, const float *g, const float *den, c
 
 // tensor-core gradient through the denominator; planes, maxima and flags are those the forward
 // pass (ctct_b200_log_matmul_tc) left in tc_ws
+// grad_f: short contraction (U+1), the output stream dominates -> three epilogue tiles in flight;
+// grad_g: long contraction (T) over the big Ef planes -> deep operand ring
+constexpr int BW_F_STAGES = 2, BW_F_EBUFS = 3, BW_G_STAGES = 4, BW_G_EBUFS = 1;
 static int den_backward_tc(const float4 *g4, const float *grad_out, const float *f, const float *g, const float *den,
                            const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
-                           float *grad_f, float *grad_g, char *ws, const TcLayout &l, cudaStream_t st) {
+                           float *grad_f, float *grad_g, char *ws, const TcLayout &l, cudaEvent_t *slot,
+                           cudaStream_t st) {
     auto *ah = reinterpret_cast<__nv_bfloat16 *>(ws + l.ah), *al = reinterpret_cast<__nv_bfloat16 *>(ws + l.al);
     auto *bh = reinterpret_cast<__nv_bfloat16 *>(ws + l.bh), *bl = reinterpret_cast<__nv_bfloat16 *>(ws + l.bl);
     auto *ph = reinterpret_cast<__nv_bfloat16 *>(ws + l.ph), *pl = reinterpret_cast<__nv_bfloat16 *>(ws + l.pl);
@@ -839,8 +856,10 @@ static int den_backward_tc(const float4 *g4, const float *grad_out, const float 
     if (rc) return rc;
     static std::once_flag attr_once;
     std::call_once(attr_once, [] {
-        cudaFuncSetAttribute(k_logmm_bwd_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BW_SMEM_BYTES);
-        cudaFuncSetAttribute(k_logmm_bwd_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BW_SMEM_BYTES);
+        cudaFuncSetAttribute(k_logmm_bwd_tc<false, BW_F_STAGES, BW_F_EBUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             bw_smem_bytes(BW_F_STAGES, BW_F_EBUFS));
+        cudaFuncSetAttribute(k_logmm_bwd_tc<true, BW_G_STAGES, BW_G_EBUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS));
     });
     CUtensorMap m_pk_h, m_pk_l, m_pm_h, m_pm_l, m_f_h, m_f_l, m_g_h, m_g_l;
     if (!make_plane_map(&m_pk_h, ph, N, T, l.Np, BW_BM) || !make_plane_map(&m_pk_l, pl, N, T, l.Np, BW_BM) ||
@@ -850,35 +869,40 @@ static int den_backward_tc(const float4 *g4, const float *grad_out, const float 
         snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "cuTensorMapEncodeTiled failed");
         return CTCT_ERR_LAUNCH;
     }
-    const unsigned vt = (unsigned)((V + BW_BN - 1) / BW_BN);
-    if (grad_f) {  // grad_f[t,v] = Ef[t,v] * sum_u P[t,u] Eg[u,v]
+    const int tiles_n = (int)((V + BW_BN - 1) / BW_BN);
+    auto launch = [&](bool a_mn, const CUtensorMap &pa_h, const CUtensorMap &pa_l, const CUtensorMap &pb_h,
+                      const CUtensorMap &pb_l, const float *src, const float *mx, float *out, int64_t M, int64_t K,
+                      const char *what) -> int {
+        CUtensorMap m_src, m_out;
+        if (!make_f32_tile_map(&m_src, src, N, M, V) || !make_f32_tile_map(&m_out, out, N, M, V)) {
+            snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "cuTensorMapEncodeTiled failed");
+            return CTCT_ERR_LAUNCH;
+        }
         LogmmBwdTcArgs a;
-        a.src = f;
-        a.mx = mf;
-        a.out = grad_f;
-        a.M = (int)T;
+        a.mx = mx;
+        a.M = (int)M;
         a.N = (int)V;
-        a.K = (int)U1;
+        a.K = (int)K;
+        a.tiles_m = (int)((M + BW_BM - 1) / BW_BM);
+        a.tiles_n = tiles_n;
+        const int64_t total = (int64_t)a.tiles_m * tiles_n * N;
+        if (total > 0x7fffffff) return CTCT_ERR_UNSUPPORTED;
+        a.total_tiles = (int)total;
         a.flags = flags;
-        dim3 grid((unsigned)((T + BW_BM - 1) / BW_BM), vt, (unsigned)N);
-        k_logmm_bwd_tc<false><<<grid, 128, BW_SMEM_BYTES, st>>>(m_pk_h, m_pk_l, m_g_h, m_g_l, a);
-        rc = check_launch("logmm_bwd_tc grad_f");
-        if (rc) return rc;
-    }
-    if (grad_g) {  // grad_g[u,v] = Eg[u,v] * sum_t P[t,u] Ef[t,v]
-        LogmmBwdTcArgs a;
-        a.src = g;
-        a.mx = mg;
-        a.out = grad_g;
-        a.M = (int)U1;
-        a.N = (int)V;
-        a.K = (int)T;
-        a.flags = flags;
-        dim3 grid((unsigned)((U1 + BW_BM - 1) / BW_BM), vt, (unsigned)N);
-        k_logmm_bwd_tc<true><<<grid, 128, BW_SMEM_BYTES, st>>>(m_pm_h, m_pm_l, m_f_h, m_f_l, a);
-        rc = check_launch("logmm_bwd_tc grad_g");
-        if (rc) return rc;
-    }
+        const unsigned grid = (unsigned)(total < sm_count() ? total : sm_count());
+        if (a_mn)
+            k_logmm_bwd_tc<true, BW_G_STAGES, BW_G_EBUFS><<<grid, BW_THREADS, bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS), st>>>(
+                pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
+        else
+            k_logmm_bwd_tc<false, BW_F_STAGES, BW_F_EBUFS><<<grid, BW_THREADS, bw_smem_bytes(BW_F_STAGES, BW_F_EBUFS), st>>>(
+                pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
+        return check_launch(what);
+    };
+    // grad_f[t,v] = Ef[t,v] * sum_u P[t,u] Eg[u,v]
+    if (grad_f && (rc = launch(false, m_pk_h, m_pk_l, m_g_h, m_g_l, f, mf, grad_f, T, U1, "logmm_bwd_tc grad_f"))) return rc;
+    prof_mark(slot, 1, st);
+    // grad_g[u,v] = Eg[u,v] * sum_t P[t,u] Ef[t,v]
+    if (grad_g && (rc = launch(true, m_pm_h, m_pm_l, m_f_h, m_f_l, g, mg, grad_g, U1, T, "logmm_bwd_tc grad_g"))) return rc;
     return CTCT_OK;
 }
 
@@ -905,7 +929,7 @@ static int simple_backward_impl(const float *grads3, const float *grad_out, cons
                 (grad_f && reinterpret_cast<uintptr_t>(grad_f) % 16) || (grad_g && reinterpret_cast<uintptr_t>(grad_g) % 16))
                 return CTCT_ERR_ARG;
             int rc = den_backward_tc(g4, grad_out, f, g, den, lx, ly, N, T, U1, V, grad_f, grad_g,
-                                     static_cast<char *>(tc_ws), l, st);
+                                     static_cast<char *>(tc_ws), l, slot, st);
             if (rc) return rc;
             run_flags = reinterpret_cast<const int *>(static_cast<char *>(tc_ws) + l.flags);
         }
@@ -931,7 +955,8 @@ static int simple_backward_impl(const float *grads3, const float *grad_out, cons
         if (grad_f && cudaMemsetAsync(grad_f, 0, sizeof(float) * N * T * V, st) != cudaSuccess) return check_launch("memset grad_f");
         if (grad_g && cudaMemsetAsync(grad_g, 0, sizeof(float) * N * U1 * V, st) != cudaSuccess) return check_launch("memset grad_g");
     }
-    prof_mark(slot, 1, st);
+    if (!(den && tc_ws)) prof_mark(slot, 1, st);  // without the tensor-core path the second interval is empty
+    prof_mark(slot, 2, st);
     PatchArgs p;
     p.grads3 = g4;
     p.scale = grad_out;
@@ -955,7 +980,7 @@ static int simple_backward_impl(const float *grads3, const float *grad_out, cons
         int rc = check_launch("simple_patch_g");
         if (rc) return rc;
     }
-    prof_mark(slot, 2, st);
+    prof_mark(slot, 3, st);
     return CTCT_OK;
 }
 
@@ -1015,7 +1040,7 @@ int ctct_b200_profile_read(float *ms, int *kind, int capacity) {
     for (int i = 0; i < n; ++i) {
         cudaEvent_t *e = g_prof.ev + 4 * i;
         const int k_ = g_prof.kind[i];
-        const int pairs = (k_ == 0 || k_ == 3 || k_ == 4) ? 3 : (k_ == 5 ? 2 : 1);  // intervals recorded per kind
+        const int pairs = (k_ == 0 || k_ >= 3) ? 3 : 1;  // intervals recorded per kind
         if (cudaEventSynchronize(e[pairs]) != cudaSuccess) return check_launch("profile sync");
         kind[i] = g_prof.kind[i];
         for (int k = 0; k < 3; ++k) {

@@ -13,22 +13,29 @@
 // work, and the kernels are bound by reading f (g) and writing grad_f (grad_g) once.
 //
 //  k_den_weights   : P as two bf16 planes (hi + lo), rows padded to a multiple of 8 columns
-//  k_logmm_bwd_tc  : one CTA per 128 x 64 output tile; A_MN = false: A = P (K-major, k = u),
-//                    A_MN = true: A = P read transposed (MN-major, m = u, k = t).  The B operand
-//                    (Eg or Ef planes) is MN-major in both: the vocabulary index is contiguous.
-//                    Two CTAs fit one SM (96 KB of stages each), so one tile's epilogue overlaps
-//                    the other's loads.  Waits are bounded as in k_logmm_tc.
+//  k_logmm_bwd_tc  : persistent, one CTA per SM walking 128 x 64 output tiles.  A_MN = false:
+//                    A = P (K-major, k = u); A_MN = true: A = P read transposed (MN-major, m = u,
+//                    k = t).  The B operand (Eg or Ef planes) is MN-major in both: the vocabulary
+//                    index is contiguous.  Warp 0 = TMA producer (operand ring + the fp32 src tile
+//                    of the epilogue), warp 1 = MMA issuer, warps 2-9 = epilogue.  Two TMEM
+//                    accumulators and two epilogue tiles, so tile i's epilogue (tcgen05.ld,
+//                    exp, TMA store) overlaps tile i+1's loads and MMAs.  All global traffic is
+//                    TMA.  Waits are bounded as in k_logmm_tc.
 #pragma once
 
 #include "logmm_tc.cuh"
 
 namespace ctct {
 
-constexpr int BW_BM = 128, BW_BN = 64, BW_BK = 64, BW_STAGES = 2;
+constexpr int BW_BM = 128, BW_BN = 64, BW_BK = 64;
 constexpr int BW_A_PLANE = BW_BM * BW_BK * 2;  // 16 KB
 constexpr int BW_B_PLANE = BW_BN * BW_BK * 2;  //  8 KB
 constexpr int BW_STAGE_BYTES = 2 * BW_A_PLANE + 2 * BW_B_PLANE;
-constexpr int BW_SMEM_BYTES = BW_STAGES * BW_STAGE_BYTES + 1024 + 128;
+constexpr int BW_EPI_HALF = BW_BM * 128;       // 128 rows x 32 floats, 128-byte swizzle
+constexpr int BW_EPI_BYTES = 2 * BW_EPI_HALF;  // one 128 x 64 fp32 tile
+constexpr int BW_EPI_WARPS = 8;                // two per TMEM lane quarter: 32 of the 64 columns each
+constexpr int BW_THREADS = 64 + 32 * BW_EPI_WARPS;
+constexpr int bw_smem_bytes(int stages, int ebufs) { return stages * BW_STAGE_BYTES + ebufs * BW_EPI_BYTES + 1024 + 256; }
 
 struct DenWeightArgs {
     const float4 *grads3;  // [B][T][U1] records {g0,g1,g2,0}; w = -scale[b] * (g0+g1+g2)
@@ -64,49 +71,66 @@ __global__ void __launch_bounds__(128) k_den_weights(const DenWeightArgs a) {
     }
 }
 
+
 struct LogmmBwdTcArgs {
-    const float *src;  // (B, M, N) fp32: f for grad_f, g for grad_g
     const float *mx;   // (B, M) row maxima of src
-    float *out;        // (B, M, N)
     int M, N, K;       // output rows per batch entry, vocabulary, contraction length
+    int tiles_m, tiles_n, total_tiles;  // total = tiles_m * tiles_n * B; m runs fastest
     int *flags;        // [0] a bounded wait ran out, [1] forward underflow (exact kernel needed)
 };
 
-template <bool A_MN>
-__global__ void __launch_bounds__(128) k_logmm_bwd_tc(const __grid_constant__ CUtensorMap map_ah,
-                                                      const __grid_constant__ CUtensorMap map_al,
-                                                      const __grid_constant__ CUtensorMap map_bh,
-                                                      const __grid_constant__ CUtensorMap map_bl,
-                                                      const LogmmBwdTcArgs a) {
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, unsigned src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+
+// maps: A planes (hi, lo), B planes (hi, lo), src (fp32, read), out (fp32, written); the last two
+// describe (B, M, N) tensors with a 32 x 128 x 1 box and 128-byte swizzle
+// STAGES: depth of the operand ring; EBUFS: epilogue tiles in flight (src loaded, result stored in place)
+template <bool A_MN, int STAGES, int EBUFS>
+__global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_constant__ CUtensorMap map_ah,
+                                                                const __grid_constant__ CUtensorMap map_al,
+                                                                const __grid_constant__ CUtensorMap map_bh,
+                                                                const __grid_constant__ CUtensorMap map_bl,
+                                                                const __grid_constant__ CUtensorMap map_src,
+                                                                const __grid_constant__ CUtensorMap map_out,
+                                                                const LogmmBwdTcArgs a) {
     extern __shared__ unsigned char bw_raw[];
     __shared__ int skip;
     if (threadIdx.x == 0) skip = a.flags[0] | a.flags[1];
     __syncthreads();
     if (skip) return;  // the exact kernel does the work (same decision for the whole CTA)
     const unsigned raw = smem_u32(bw_raw);
-    const unsigned tiles = (raw + 1023u) & ~1023u;
-    const unsigned bars = tiles + BW_STAGES * BW_STAGE_BYTES;
+    const unsigned ring = (raw + 1023u) & ~1023u;
+    const unsigned epi = ring + STAGES * BW_STAGE_BYTES;
+    const unsigned bars = epi + EBUFS * BW_EPI_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (BW_STAGES + s); };
-    const unsigned accum_bar = bars + 8u * (2 * BW_STAGES);
-    const unsigned slot_addr = bars + 8u * (2 * BW_STAGES + 1);
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto acc_full = [&](int q) { return bars + 8u * (2 * STAGES + q); };
+    auto acc_empty = [&](int q) { return bars + 8u * (2 * STAGES + 2 + q); };
+    auto src_full = [&](int e) { return bars + 8u * (2 * STAGES + 4 + e); };
+    auto src_empty = [&](int e) { return bars + 8u * (2 * STAGES + 4 + EBUFS + e); };
+    constexpr int NBARS = 2 * STAGES + 4 + 2 * EBUFS;
+    static_assert(8 * NBARS + 8 <= 256, "barrier area");
+    const unsigned slot_addr = bars + 8u * NBARS;
     unsigned *slot_ptr = reinterpret_cast<unsigned *>(bw_raw + (slot_addr - raw));
+    unsigned char *epi_ptr = bw_raw + (epi - raw);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BW_BM, n0 = blockIdx.y * BW_BN, b = blockIdx.z;
     const int nk = (a.K + BW_BK - 1) / BW_BK;
+    constexpr unsigned TMEM_COLS = 2 * BW_BN;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < BW_STAGES; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
-        }
-        mbar_init(accum_bar, 1);
+        for (int q = 0; q < NBARS; ++q) mbar_init(bars + 8u * q, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
         __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(BW_BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -115,103 +139,173 @@ __global__ void __launch_bounds__(128) k_logmm_bwd_tc(const __grid_constant__ CU
     const unsigned tmem_base = *slot_ptr;
     bool ok = true;
 
+    auto tile_coords = [&](int tile, int &m0, int &n0, int &b) {
+        const int mt = tile % a.tiles_m;
+        const int rest = tile / a.tiles_m;
+        m0 = mt * BW_BM;
+        n0 = (rest % a.tiles_n) * BW_BN;
+        b = rest / a.tiles_n;
+    };
+
     if (warp == 0 && lane == 0) {
-        // ---- TMA producer
-        for (int kb = 0; kb < nk && ok; ++kb) {
-            const int s = kb % BW_STAGES;
-            ok = mbar_wait(empty_bar(s), ((kb / BW_STAGES) & 1) ^ 1);
-            if (!ok) break;
-            const unsigned st = tiles + s * BW_STAGE_BYTES;
-            const unsigned bar = full_bar(s);
-            mbar_expect_tx(bar, BW_STAGE_BYTES);
-            if (A_MN) {  // two 64-wide chunks of m per plane, each 64 k-rows of 128 bytes
-                tma_load_3d(st, &map_ah, bar, m0, kb * BW_BK, b);
-                tma_load_3d(st + BW_A_PLANE / 2, &map_ah, bar, m0 + 64, kb * BW_BK, b);
-                tma_load_3d(st + BW_A_PLANE, &map_al, bar, m0, kb * BW_BK, b);
-                tma_load_3d(st + BW_A_PLANE + BW_A_PLANE / 2, &map_al, bar, m0 + 64, kb * BW_BK, b);
-            } else {     // 128 m-rows of 64 k (128 bytes)
-                tma_load_3d(st, &map_ah, bar, kb * BW_BK, m0, b);
-                tma_load_3d(st + BW_A_PLANE, &map_al, bar, kb * BW_BK, m0, b);
+        // ---- TMA producer: per tile the operand k-blocks, then the fp32 src tile of the epilogue
+        unsigned it = 0;
+        unsigned armed = 0, armed_parity = 0;  // bit s: full_bar(s) armed / parity of that phase; bits 8..: src_full
+        for (int tile = blockIdx.x, i = 0; tile < a.total_tiles && ok; tile += gridDim.x, ++i) {
+            int m0, n0, b;
+            tile_coords(tile, m0, n0, b);
+            for (int kb = 0; kb < nk; ++kb, ++it) {
+                const int s = it % STAGES;
+                const unsigned ph = (it / STAGES) & 1;
+                ok = mbar_wait(empty_bar(s), ph ^ 1);
+                if (!ok) break;
+                const unsigned st = ring + s * BW_STAGE_BYTES;
+                const unsigned bar = full_bar(s);
+                mbar_expect_tx(bar, BW_STAGE_BYTES);
+                if (A_MN) {  // two 64-wide chunks of m per plane, each 64 k-rows of 128 bytes
+                    tma_load_3d(st, &map_ah, bar, m0, kb * BW_BK, b);
+                    tma_load_3d(st + BW_A_PLANE / 2, &map_ah, bar, m0 + 64, kb * BW_BK, b);
+                    tma_load_3d(st + BW_A_PLANE, &map_al, bar, m0, kb * BW_BK, b);
+                    tma_load_3d(st + BW_A_PLANE + BW_A_PLANE / 2, &map_al, bar, m0 + 64, kb * BW_BK, b);
+                } else {     // 128 m-rows of 64 k (128 bytes)
+                    tma_load_3d(st, &map_ah, bar, kb * BW_BK, m0, b);
+                    tma_load_3d(st + BW_A_PLANE, &map_al, bar, kb * BW_BK, m0, b);
+                }
+                tma_load_3d(st + 2 * BW_A_PLANE, &map_bh, bar, n0, kb * BW_BK, b);
+                tma_load_3d(st + 2 * BW_A_PLANE + BW_B_PLANE, &map_bl, bar, n0, kb * BW_BK, b);
+                armed |= 1u << s;
+                armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
             }
-            tma_load_3d(st + 2 * BW_A_PLANE, &map_bh, bar, n0, kb * BW_BK, b);
-            tma_load_3d(st + 2 * BW_A_PLANE + BW_B_PLANE, &map_bl, bar, n0, kb * BW_BK, b);
+            if (!ok) break;
+            const int e = i % EBUFS;
+            const unsigned eph = (i / EBUFS) & 1;
+            ok = mbar_wait(src_empty(e), eph ^ 1);
+            if (!ok) break;
+            mbar_expect_tx(src_full(e), BW_EPI_BYTES);
+            tma_load_3d(epi + e * BW_EPI_BYTES, &map_src, src_full(e), n0, m0, b);
+            tma_load_3d(epi + e * BW_EPI_BYTES + BW_EPI_HALF, &map_src, src_full(e), n0 + 32, m0, b);
+            armed |= 1u << (8 + e);
+            armed_parity = (armed_parity & ~(1u << (8 + e))) | (eph << (8 + e));
         }
         if (!ok) atomicExch(a.flags, 1);
+        // no copy of this CTA may still be in flight when it exits (bounded; immediate when all went well)
+        for (int s = 0; s < STAGES; ++s)
+            if (armed & (1u << s)) mbar_wait(full_bar(s), (armed_parity >> s) & 1);
+        for (int e = 0; e < EBUFS; ++e)
+            if (armed & (1u << (8 + e))) mbar_wait(src_full(e), (armed_parity >> (8 + e)) & 1);
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: D[128 x 64] += A[128 x 16] * B[16 x 64]; B is MN-major, A as templated
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | (A_MN ? (1u << 15) : 0u) | (1u << 16) |
                                (static_cast<unsigned>(BW_BN >> 3) << 17) | (static_cast<unsigned>(BW_BM >> 4) << 24);
-        for (int kb = 0; kb < nk && ok; ++kb) {
-            const int s = kb % BW_STAGES;
-            ok = mbar_wait(full_bar(s), (kb / BW_STAGES) & 1);
+        unsigned it = 0;
+        for (int tile = blockIdx.x, i = 0; tile < a.total_tiles && ok; tile += gridDim.x, ++i) {
+            const int q = i & 1;
+            ok = mbar_wait(acc_empty(q), ((i >> 1) & 1) ^ 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned st = tiles + s * BW_STAGE_BYTES;
+            const unsigned acc = tmem_base + static_cast<unsigned>(q) * BW_BN;
+            for (int kb = 0; kb < nk; ++kb, ++it) {
+                const int s = it % STAGES;
+                ok = mbar_wait(full_bar(s), (it / STAGES) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned st = ring + s * BW_STAGE_BYTES;
 #pragma unroll
-            for (int k4 = 0; k4 < BW_BK / 16; ++k4) {
-                uint64_t ah, al;
-                if (A_MN) {
-                    ah = umma_desc_mn(st + k4 * 2048, BW_A_PLANE / 2);
-                    al = umma_desc_mn(st + BW_A_PLANE + k4 * 2048, BW_A_PLANE / 2);
-                } else {
-                    ah = umma_desc(st + k4 * 32);
-                    al = umma_desc(st + BW_A_PLANE + k4 * 32);
+                for (int k4 = 0; k4 < BW_BK / 16; ++k4) {
+                    uint64_t ah, al;
+                    if (A_MN) {
+                        ah = umma_desc_mn(st + k4 * 2048, BW_A_PLANE / 2);
+                        al = umma_desc_mn(st + BW_A_PLANE + k4 * 2048, BW_A_PLANE / 2);
+                    } else {
+                        ah = umma_desc(st + k4 * 32);
+                        al = umma_desc(st + BW_A_PLANE + k4 * 32);
+                    }
+                    const uint64_t bh = umma_desc_mn(st + 2 * BW_A_PLANE + k4 * 2048, BW_B_PLANE);
+                    const uint64_t bl = umma_desc_mn(st + 2 * BW_A_PLANE + BW_B_PLANE + k4 * 2048, BW_B_PLANE);
+                    umma_bf16(acc, ah, bh, idesc, (kb | k4) ? 1u : 0u);
+                    umma_bf16(acc, ah, bl, idesc, 1u);
+                    umma_bf16(acc, al, bh, idesc, 1u);
                 }
-                const uint64_t bh = umma_desc_mn(st + 2 * BW_A_PLANE + k4 * 2048, BW_B_PLANE);
-                const uint64_t bl = umma_desc_mn(st + 2 * BW_A_PLANE + BW_B_PLANE + k4 * 2048, BW_B_PLANE);
-                umma_bf16(tmem_base, ah, bh, idesc, (kb | k4) ? 1u : 0u);
-                umma_bf16(tmem_base, ah, bl, idesc, 1u);
-                umma_bf16(tmem_base, al, bh, idesc, 1u);
+                umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
             }
-            umma_commit(empty_bar(s));
+            if (ok) umma_commit(acc_full(q));
         }
-        if (ok) umma_commit(accum_bar);
-        else atomicExch(a.flags, 1);
-    }
-    __syncwarp();
-
-    // ---- epilogue: out = exp(src - mx) * D; warp w owns TMEM lanes (= output rows) [32w, 32w+32)
-    const int row = m0 + warp * 32 + lane;
-    const int64_t base = (static_cast<int64_t>(b) * a.M + row) * a.N + n0;
-    float mxl = 0.0f;
-    if (row < a.M) mxl = a.mx[static_cast<int64_t>(b) * a.M + row];
-    const bool done = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0));
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (done) {
-#pragma unroll 1
-        for (int c = 0; c < BW_BN / 32; ++c) {
-            unsigned v[32];
-            tmem_ld_32x32(tmem_base + (static_cast<unsigned>(warp * 32) << 16) + c * 32, v);
-            if (row < a.M) {
-                const float4 *src = reinterpret_cast<const float4 *>(a.src + base + c * 32);
-                float4 *dst = reinterpret_cast<float4 *>(a.out + base + c * 32);
-                float4 x[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    x[j] = (n0 + c * 32 + 4 * j < a.N) ? __ldg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!ok) atomicExch(a.flags, 1);
+    } else if (warp >= 2) {
+        // ---- epilogue warps: out = exp(src - mx) * D, in place in the src tile, then one TMA store.
+        // A warp may read the TMEM lanes [32 * (warp % 4), +32): one tile row per thread; the two
+        // warps of a lane quarter take 32 columns each.
+        const int part = warp & 3;
+        const int c = (warp - 2) >> 2;
+        const int r = part * 32 + lane;
+        const bool leader = (threadIdx.x == 64);
+        constexpr int PENDING = EBUFS >= 2 ? 1 : 0;  // stores that may still be reading their tile
+        for (int tile = blockIdx.x, i = 0; tile < a.total_tiles; tile += gridDim.x, ++i) {
+            int m0, n0, b;
+            tile_coords(tile, m0, n0, b);
+            const int q = i & 1;
+            const int e = i % EBUFS;
+            float mxr = 0.0f;
+            if (m0 + r < a.M) mxr = __ldg(a.mx + static_cast<int64_t>(b) * a.M + m0 + r);
+            bool got = mbar_wait(src_full(e), (i / EBUFS) & 1);
+            got = got && mbar_wait(acc_full(q), (i >> 1) & 1);
+            // same decision in all epilogue warps (they meet again at a barrier below)
+            unsigned all_got;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.u32 q, %1, 0;\n\t"
+                "bar.red.and.pred p, 1, %2, q;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(all_got)
+                : "r"(static_cast<unsigned>(got)), "n"(32 * BW_EPI_WARPS)
+                : "memory");
+            ok = all_got != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            {
+                unsigned v[32];
+                tmem_ld_32x32(tmem_base + (static_cast<unsigned>(part * 32) << 16) + q * BW_BN + c * 32, v);
+                unsigned char *rowp = epi_ptr + e * BW_EPI_BYTES + c * BW_EPI_HALF + r * 128;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    if (n0 + c * 32 + 4 * j < a.N) {
-                        float4 r;
-                        // a zero sum stays zero even where exp() would overflow or src is -inf
-                        const float d0 = __uint_as_float(v[4 * j]), d1 = __uint_as_float(v[4 * j + 1]);
-                        const float d2 = __uint_as_float(v[4 * j + 2]), d3 = __uint_as_float(v[4 * j + 3]);
-                        r.x = d0 != 0.0f ? d0 * ex2((x[j].x - mxl) * LOG2E) : 0.0f;
-                        r.y = d1 != 0.0f ? d1 * ex2((x[j].y - mxl) * LOG2E) : 0.0f;
-                        r.z = d2 != 0.0f ? d2 * ex2((x[j].z - mxl) * LOG2E) : 0.0f;
-                        r.w = d3 != 0.0f ? d3 * ex2((x[j].w - mxl) * LOG2E) : 0.0f;
-                        dst[j] = r;
-                    }
+                    float4 *cell = reinterpret_cast<float4 *>(rowp + ((j ^ (r & 7)) << 4));  // 128-byte swizzle
+                    const float4 x = *cell;
+                    // a zero sum stays zero even where exp() would overflow or src is -inf
+                    const float d0 = __uint_as_float(v[4 * j]), d1 = __uint_as_float(v[4 * j + 1]);
+                    const float d2 = __uint_as_float(v[4 * j + 2]), d3 = __uint_as_float(v[4 * j + 3]);
+                    float4 o;
+                    o.x = d0 != 0.0f ? d0 * ex2((x.x - mxr) * LOG2E) : 0.0f;
+                    o.y = d1 != 0.0f ? d1 * ex2((x.y - mxr) * LOG2E) : 0.0f;
+                    o.z = d2 != 0.0f ? d2 * ex2((x.z - mxr) * LOG2E) : 0.0f;
+                    o.w = d3 != 0.0f ? d3 * ex2((x.w - mxr) * LOG2E) : 0.0f;
+                    *cell = o;
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tile writes -> visible to the TMA store
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * BW_EPI_WARPS) : "memory");  // the epilogue warps
+            if (leader) {
+                mbar_arrive(acc_empty(q));  // every epilogue warp has read this accumulator
+                tma_store_3d(&map_out, epi + e * BW_EPI_BYTES, n0, m0, b);
+                tma_store_3d(&map_out, epi + e * BW_EPI_BYTES + BW_EPI_HALF, n0 + 32, m0, b);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                if (i >= PENDING) {
+                    // the store issued PENDING tiles ago has finished reading its buffer: hand it back
+                    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
+                    mbar_arrive(src_empty((i - PENDING) % EBUFS));
                 }
             }
         }
-    } else if (threadIdx.x == 0) {
-        atomicExch(a.flags, 1);
+        if (leader) {
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            if (!ok) atomicExch(a.flags, 1);
+        }
     }
+    __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BW_BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
