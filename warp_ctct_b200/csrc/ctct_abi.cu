@@ -828,6 +828,8 @@ int ctct_b200_simple_forward(const float *f, const float *g, const float *den, c
 // grad_f: short contraction (U+1), the output stream dominates -> three epilogue tiles in flight;
 // grad_g: long contraction (T) over the big Ef planes -> deep operand ring
 constexpr int BW_F_STAGES = 2, BW_F_EBUFS = 3, BW_G_STAGES = 4, BW_G_EBUFS = 1;
+// grad_f with U+1 <= 128: the weight tile stays in shared memory (64 KB), only Eg streams (16 KB stages)
+constexpr int BW_R_STAGES = 4, BW_R_EBUFS = 3;
 static int den_backward_tc(const float4 *g4, const float *grad_out, const float *f, const float *g, const float *den,
                            const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
                            float *grad_f, float *grad_g, char *ws, const TcLayout &l, cudaEvent_t *slot,
@@ -856,10 +858,12 @@ static int den_backward_tc(const float4 *g4, const float *grad_out, const float 
     if (rc) return rc;
     static std::once_flag attr_once;
     std::call_once(attr_once, [] {
-        cudaFuncSetAttribute(k_logmm_bwd_tc<false, BW_F_STAGES, BW_F_EBUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             bw_smem_bytes(BW_F_STAGES, BW_F_EBUFS));
-        cudaFuncSetAttribute(k_logmm_bwd_tc<true, BW_G_STAGES, BW_G_EBUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS));
+        cudaFuncSetAttribute(k_logmm_bwd_tc<false, false, BW_F_STAGES, BW_F_EBUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             bw_smem_bytes(BW_F_STAGES, BW_F_EBUFS, false));
+        cudaFuncSetAttribute(k_logmm_bwd_tc<false, true, BW_R_STAGES, BW_R_EBUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             bw_smem_bytes(BW_R_STAGES, BW_R_EBUFS, true));
+        cudaFuncSetAttribute(k_logmm_bwd_tc<true, false, BW_G_STAGES, BW_G_EBUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS, false));
     });
     CUtensorMap m_pk_h, m_pk_l, m_pm_h, m_pm_l, m_f_h, m_f_l, m_g_h, m_g_l;
     if (!make_plane_map(&m_pk_h, ph, N, T, l.Np, BW_BM) || !make_plane_map(&m_pk_l, pl, N, T, l.Np, BW_BM) ||
@@ -891,11 +895,14 @@ static int den_backward_tc(const float4 *g4, const float *grad_out, const float 
         a.flags = flags;
         const unsigned grid = (unsigned)(total < sm_count() ? total : sm_count());
         if (a_mn)
-            k_logmm_bwd_tc<true, BW_G_STAGES, BW_G_EBUFS><<<grid, BW_THREADS, bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS), st>>>(
-                pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
+            k_logmm_bwd_tc<true, false, BW_G_STAGES, BW_G_EBUFS>
+                <<<grid, BW_THREADS, bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS, false), st>>>(pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
+        else if (K <= BW_BK * BW_ARES_KB)  // the whole contraction of A fits the resident buffer
+            k_logmm_bwd_tc<false, true, BW_R_STAGES, BW_R_EBUFS>
+                <<<grid, BW_THREADS, bw_smem_bytes(BW_R_STAGES, BW_R_EBUFS, true), st>>>(pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
         else
-            k_logmm_bwd_tc<false, BW_F_STAGES, BW_F_EBUFS><<<grid, BW_THREADS, bw_smem_bytes(BW_F_STAGES, BW_F_EBUFS), st>>>(
-                pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
+            k_logmm_bwd_tc<false, false, BW_F_STAGES, BW_F_EBUFS>
+                <<<grid, BW_THREADS, bw_smem_bytes(BW_F_STAGES, BW_F_EBUFS, false), st>>>(pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
         return check_launch(what);
     };
     // grad_f[t,v] = Ef[t,v] * sum_u P[t,u] Eg[u,v]

@@ -35,7 +35,11 @@ constexpr int BW_EPI_HALF = BW_BM * 128;       // 128 rows x 32 floats, 128-byte
 constexpr int BW_EPI_BYTES = 2 * BW_EPI_HALF;  // one 128 x 64 fp32 tile
 constexpr int BW_EPI_WARPS = 8;                // two per TMEM lane quarter: 32 of the 64 columns each
 constexpr int BW_THREADS = 64 + 32 * BW_EPI_WARPS;
-constexpr int bw_smem_bytes(int stages, int ebufs) { return stages * BW_STAGE_BYTES + ebufs * BW_EPI_BYTES + 1024 + 256; }
+constexpr int BW_ARES_KB = 2;                  // k-blocks of A that the resident variant keeps in shared memory
+__host__ __device__ constexpr int bw_stage_bytes(bool a_res) { return a_res ? 2 * BW_B_PLANE : BW_STAGE_BYTES; }
+constexpr int bw_smem_bytes(int stages, int ebufs, bool a_res) {
+    return stages * bw_stage_bytes(a_res) + (a_res ? BW_ARES_KB * 2 * BW_A_PLANE : 0) + ebufs * BW_EPI_BYTES + 1024 + 256;
+}
 
 struct DenWeightArgs {
     const float4 *grads3;  // [B][T][U1] records {g0,g1,g2,0}; w = -scale[b] * (g0+g1+g2)
@@ -90,8 +94,11 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, unsigned sr
 
 // maps: A planes (hi, lo), B planes (hi, lo), src (fp32, read), out (fp32, written); the last two
 // describe (B, M, N) tensors with a 32 x 128 x 1 box and 128-byte swizzle
-// STAGES: depth of the operand ring; EBUFS: epilogue tiles in flight (src loaded, result stored in place)
-template <bool A_MN, int STAGES, int EBUFS>
+// STAGES: depth of the operand ring; EBUFS: epilogue tiles in flight (src loaded, result stored in place).
+// A_RES (K-major A, K <= 64 * BW_ARES_KB): each CTA takes a contiguous run of tiles with n fastest
+// and keeps the A tile of the current (batch entry, m-tile) in shared memory, so that only B
+// streams through the ring; otherwise tiles are dealt round-robin with m fastest.
+template <bool A_MN, bool A_RES, int STAGES, int EBUFS>
 __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_constant__ CUtensorMap map_ah,
                                                                 const __grid_constant__ CUtensorMap map_al,
                                                                 const __grid_constant__ CUtensorMap map_bh,
@@ -105,8 +112,12 @@ __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_con
     __syncthreads();
     if (skip) return;  // the exact kernel does the work (same decision for the whole CTA)
     const unsigned raw = smem_u32(bw_raw);
+    static_assert(!(A_RES && A_MN), "the resident A tile is K-major");
+    constexpr int STAGE_BYTES = bw_stage_bytes(A_RES);
+    constexpr int B_OFF = A_RES ? 0 : 2 * BW_A_PLANE;  // B planes inside a ring stage
     const unsigned ring = (raw + 1023u) & ~1023u;
-    const unsigned epi = ring + STAGES * BW_STAGE_BYTES;
+    const unsigned ares = ring + STAGES * STAGE_BYTES;  // resident A: per k-block hi plane, lo plane
+    const unsigned epi = ares + (A_RES ? BW_ARES_KB * 2 * BW_A_PLANE : 0);
     const unsigned bars = epi + EBUFS * BW_EPI_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
@@ -114,7 +125,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_con
     auto acc_empty = [&](int q) { return bars + 8u * (2 * STAGES + 2 + q); };
     auto src_full = [&](int e) { return bars + 8u * (2 * STAGES + 4 + e); };
     auto src_empty = [&](int e) { return bars + 8u * (2 * STAGES + 4 + EBUFS + e); };
-    constexpr int NBARS = 2 * STAGES + 4 + 2 * EBUFS;
+    const unsigned a_full = bars + 8u * (2 * STAGES + 4 + 2 * EBUFS), a_empty = a_full + 8u;
+    constexpr int NBARS = 2 * STAGES + 4 + 2 * EBUFS + 2;
     static_assert(8 * NBARS + 8 <= 256, "barrier area");
     const unsigned slot_addr = bars + 8u * NBARS;
     unsigned *slot_ptr = reinterpret_cast<unsigned *>(bw_raw + (slot_addr - raw));
@@ -139,30 +151,57 @@ __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_con
     const unsigned tmem_base = *slot_ptr;
     bool ok = true;
 
+    // this CTA's tiles: first, first + step, ... < last
+    const int first = A_RES ? static_cast<int>(static_cast<int64_t>(blockIdx.x) * a.total_tiles / gridDim.x) : blockIdx.x;
+    const int last = A_RES ? static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * a.total_tiles / gridDim.x) : a.total_tiles;
+    const int step = A_RES ? 1 : gridDim.x;
     auto tile_coords = [&](int tile, int &m0, int &n0, int &b) {
-        const int mt = tile % a.tiles_m;
-        const int rest = tile / a.tiles_m;
-        m0 = mt * BW_BM;
-        n0 = (rest % a.tiles_n) * BW_BN;
-        b = rest / a.tiles_n;
+        if (A_RES) {  // n fastest; tile / tiles_n names the (b, m-tile) group that shares A
+            n0 = (tile % a.tiles_n) * BW_BN;
+            const int rest = tile / a.tiles_n;
+            m0 = (rest % a.tiles_m) * BW_BM;
+            b = rest / a.tiles_m;
+        } else {
+            m0 = (tile % a.tiles_m) * BW_BM;
+            const int rest = tile / a.tiles_m;
+            n0 = (rest % a.tiles_n) * BW_BN;
+            b = rest / a.tiles_n;
+        }
     };
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer: per tile the operand k-blocks, then the fp32 src tile of the epilogue
         unsigned it = 0;
         unsigned armed = 0, armed_parity = 0;  // bit s: full_bar(s) armed / parity of that phase; bits 8..: src_full
-        for (int tile = blockIdx.x, i = 0; tile < a.total_tiles && ok; tile += gridDim.x, ++i) {
+        int group = -1;
+        unsigned groups = 0;
+        for (int tile = first, i = 0; tile < last && ok; tile += step, ++i) {
             int m0, n0, b;
             tile_coords(tile, m0, n0, b);
+            if (A_RES && tile / a.tiles_n != group) {
+                // new (batch entry, m-tile): reload A once the MMAs on the old one have finished
+                group = tile / a.tiles_n;
+                ok = mbar_wait(a_empty, (groups & 1) ^ 1);
+                if (!ok) break;
+                mbar_expect_tx(a_full, nk * 2 * BW_A_PLANE);
+                for (int kb = 0; kb < nk; ++kb) {
+                    tma_load_3d(ares + kb * 2 * BW_A_PLANE, &map_ah, a_full, kb * BW_BK, m0, b);
+                    tma_load_3d(ares + kb * 2 * BW_A_PLANE + BW_A_PLANE, &map_al, a_full, kb * BW_BK, m0, b);
+                }
+                armed |= 1u << 16;
+                armed_parity = (armed_parity & ~(1u << 16)) | ((groups & 1) << 16);
+                ++groups;
+            }
             for (int kb = 0; kb < nk; ++kb, ++it) {
                 const int s = it % STAGES;
                 const unsigned ph = (it / STAGES) & 1;
                 ok = mbar_wait(empty_bar(s), ph ^ 1);
                 if (!ok) break;
-                const unsigned st = ring + s * BW_STAGE_BYTES;
+                const unsigned st = ring + s * STAGE_BYTES;
                 const unsigned bar = full_bar(s);
-                mbar_expect_tx(bar, BW_STAGE_BYTES);
-                if (A_MN) {  // two 64-wide chunks of m per plane, each 64 k-rows of 128 bytes
+                mbar_expect_tx(bar, STAGE_BYTES);
+                if (A_RES) {
+                } else if (A_MN) {  // two 64-wide chunks of m per plane, each 64 k-rows of 128 bytes
                     tma_load_3d(st, &map_ah, bar, m0, kb * BW_BK, b);
                     tma_load_3d(st + BW_A_PLANE / 2, &map_ah, bar, m0 + 64, kb * BW_BK, b);
                     tma_load_3d(st + BW_A_PLANE, &map_al, bar, m0, kb * BW_BK, b);
@@ -171,8 +210,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_con
                     tma_load_3d(st, &map_ah, bar, kb * BW_BK, m0, b);
                     tma_load_3d(st + BW_A_PLANE, &map_al, bar, kb * BW_BK, m0, b);
                 }
-                tma_load_3d(st + 2 * BW_A_PLANE, &map_bh, bar, n0, kb * BW_BK, b);
-                tma_load_3d(st + 2 * BW_A_PLANE + BW_B_PLANE, &map_bl, bar, n0, kb * BW_BK, b);
+                tma_load_3d(st + B_OFF, &map_bh, bar, n0, kb * BW_BK, b);
+                tma_load_3d(st + B_OFF + BW_B_PLANE, &map_bl, bar, n0, kb * BW_BK, b);
                 armed |= 1u << s;
                 armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
             }
@@ -193,13 +232,22 @@ __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_con
             if (armed & (1u << s)) mbar_wait(full_bar(s), (armed_parity >> s) & 1);
         for (int e = 0; e < EBUFS; ++e)
             if (armed & (1u << (8 + e))) mbar_wait(src_full(e), (armed_parity >> (8 + e)) & 1);
+        if (armed & (1u << 16)) mbar_wait(a_full, (armed_parity >> 16) & 1);
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: D[128 x 64] += A[128 x 16] * B[16 x 64]; B is MN-major, A as templated
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | (A_MN ? (1u << 15) : 0u) | (1u << 16) |
                                (static_cast<unsigned>(BW_BN >> 3) << 17) | (static_cast<unsigned>(BW_BM >> 4) << 24);
         unsigned it = 0;
-        for (int tile = blockIdx.x, i = 0; tile < a.total_tiles && ok; tile += gridDim.x, ++i) {
+        int group = -1;
+        unsigned groups = 0;
+        for (int tile = first, i = 0; tile < last && ok; tile += step, ++i) {
             const int q = i & 1;
+            if (A_RES && tile / a.tiles_n != group) {
+                group = tile / a.tiles_n;
+                ok = mbar_wait(a_full, groups & 1);
+                if (!ok) break;
+                ++groups;
+            }
             ok = mbar_wait(acc_empty(q), ((i >> 1) & 1) ^ 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -209,19 +257,22 @@ __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_con
                 ok = mbar_wait(full_bar(s), (it / STAGES) & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned st = ring + s * BW_STAGE_BYTES;
+                const unsigned st = ring + s * STAGE_BYTES;
 #pragma unroll
                 for (int k4 = 0; k4 < BW_BK / 16; ++k4) {
                     uint64_t ah, al;
-                    if (A_MN) {
+                    if (A_RES) {
+                        ah = umma_desc(ares + kb * 2 * BW_A_PLANE + k4 * 32);
+                        al = umma_desc(ares + kb * 2 * BW_A_PLANE + BW_A_PLANE + k4 * 32);
+                    } else if (A_MN) {
                         ah = umma_desc_mn(st + k4 * 2048, BW_A_PLANE / 2);
                         al = umma_desc_mn(st + BW_A_PLANE + k4 * 2048, BW_A_PLANE / 2);
                     } else {
                         ah = umma_desc(st + k4 * 32);
                         al = umma_desc(st + BW_A_PLANE + k4 * 32);
                     }
-                    const uint64_t bh = umma_desc_mn(st + 2 * BW_A_PLANE + k4 * 2048, BW_B_PLANE);
-                    const uint64_t bl = umma_desc_mn(st + 2 * BW_A_PLANE + BW_B_PLANE + k4 * 2048, BW_B_PLANE);
+                    const uint64_t bh = umma_desc_mn(st + B_OFF + k4 * 2048, BW_B_PLANE);
+                    const uint64_t bl = umma_desc_mn(st + B_OFF + BW_B_PLANE + k4 * 2048, BW_B_PLANE);
                     umma_bf16(acc, ah, bh, idesc, (kb | k4) ? 1u : 0u);
                     umma_bf16(acc, ah, bl, idesc, 1u);
                     umma_bf16(acc, al, bh, idesc, 1u);
@@ -229,6 +280,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_con
                 umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
             }
             if (ok) umma_commit(acc_full(q));
+            // last tile on this A: let the producer overwrite it once these MMAs are done
+            if (A_RES && ok && (tile + 1 >= last || (tile + 1) / a.tiles_n != group)) umma_commit(a_empty);
         }
         if (!ok) atomicExch(a.flags, 1);
     } else if (warp >= 2) {
@@ -240,7 +293,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_con
         const int r = part * 32 + lane;
         const bool leader = (threadIdx.x == 64);
         constexpr int PENDING = EBUFS >= 2 ? 1 : 0;  // stores that may still be reading their tile
-        for (int tile = blockIdx.x, i = 0; tile < a.total_tiles; tile += gridDim.x, ++i) {
+        for (int tile = first, i = 0; tile < last; tile += step, ++i) {
             int m0, n0, b;
             tile_coords(tile, m0, n0, b);
             const int q = i & 1;
