@@ -258,21 +258,18 @@ __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_con
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned st = ring + s * STAGE_BYTES;
+                // low descriptor words of the hi planes; lo planes and k-steps are constant offsets away
+                const unsigned da = A_RES  ? umma_lo(ares + kb * 2 * BW_A_PLANE)
+                                    : A_MN ? umma_lo_mn(st, BW_A_PLANE / 2)
+                                           : umma_lo(st);
+                const unsigned db = umma_lo_mn(st + B_OFF, BW_B_PLANE);
+                constexpr unsigned A_KSTEP = (A_MN ? 2048 : 32) / 16, B_KSTEP = 2048 / 16;
 #pragma unroll
                 for (int k4 = 0; k4 < BW_BK / 16; ++k4) {
-                    uint64_t ah, al;
-                    if (A_RES) {
-                        ah = umma_desc(ares + kb * 2 * BW_A_PLANE + k4 * 32);
-                        al = umma_desc(ares + kb * 2 * BW_A_PLANE + BW_A_PLANE + k4 * 32);
-                    } else if (A_MN) {
-                        ah = umma_desc_mn(st + k4 * 2048, BW_A_PLANE / 2);
-                        al = umma_desc_mn(st + BW_A_PLANE + k4 * 2048, BW_A_PLANE / 2);
-                    } else {
-                        ah = umma_desc(st + k4 * 32);
-                        al = umma_desc(st + BW_A_PLANE + k4 * 32);
-                    }
-                    const uint64_t bh = umma_desc_mn(st + B_OFF + k4 * 2048, BW_B_PLANE);
-                    const uint64_t bl = umma_desc_mn(st + B_OFF + BW_B_PLANE + k4 * 2048, BW_B_PLANE);
+                    const uint64_t ah = umma_pack(da + k4 * A_KSTEP);
+                    const uint64_t al = umma_pack(da + BW_A_PLANE / 16 + k4 * A_KSTEP);
+                    const uint64_t bh = umma_pack(db + k4 * B_KSTEP);
+                    const uint64_t bl = umma_pack(db + BW_B_PLANE / 16 + k4 * B_KSTEP);
                     umma_bf16(acc, ah, bh, idesc, (kb | k4) ? 1u : 0u);
                     umma_bf16(acc, ah, bl, idesc, 1u);
                     umma_bf16(acc, al, bh, idesc, 1u);

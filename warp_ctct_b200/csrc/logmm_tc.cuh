@@ -134,6 +134,19 @@ __device__ __forceinline__ uint64_t umma_desc_mn(unsigned smem_addr, unsigned lb
     d |= static_cast<uint64_t>(2) << 61;
     return d;
 }
+// The issuing thread is alone in its warp, so every instruction between two MMAs costs several
+// cycles: descriptors are kept as a 32-bit low word (start address and leading offset) that is
+// advanced with plain adds (+1 per 16 bytes) next to a constant high word.
+constexpr unsigned UMMA_DESC_HI = 64u | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, SWIZZLE_128B
+__device__ __forceinline__ unsigned umma_lo(unsigned smem_addr) { return ((smem_addr >> 4) & 0x3fffu) | (1u << 16); }
+__device__ __forceinline__ unsigned umma_lo_mn(unsigned smem_addr, unsigned lbo_bytes) {
+    return ((smem_addr >> 4) & 0x3fffu) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+__device__ __forceinline__ uint64_t umma_pack(unsigned lo) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(UMMA_DESC_HI));
+    return d;
+}
 __device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -235,12 +248,13 @@ __global__ void __launch_bounds__(128) k_logmm_tc(const __grid_constant__ CUtens
             // and the small cross terms into a fourth; the epilogue adds the four in fp32.
             const unsigned acc_main = tmem_base + static_cast<unsigned>(kb % 3) * TC_BN;
             const unsigned acc_cross = tmem_base + 3u * TC_BN;
+            const unsigned d0 = umma_lo(st);  // A_hi; the other planes follow at TC_PLANE_BYTES each
 #pragma unroll
             for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
-                const uint64_t ah = umma_desc(st + 0 * TC_PLANE_BYTES + k4 * 32);
-                const uint64_t al = umma_desc(st + 1 * TC_PLANE_BYTES + k4 * 32);
-                const uint64_t bh = umma_desc(st + 2 * TC_PLANE_BYTES + k4 * 32);
-                const uint64_t bl = umma_desc(st + 3 * TC_PLANE_BYTES + k4 * 32);
+                const uint64_t ah = umma_pack(d0 + (0 * TC_PLANE_BYTES + k4 * 32) / 16);
+                const uint64_t al = umma_pack(d0 + (1 * TC_PLANE_BYTES + k4 * 32) / 16);
+                const uint64_t bh = umma_pack(d0 + (2 * TC_PLANE_BYTES + k4 * 32) / 16);
+                const uint64_t bl = umma_pack(d0 + (3 * TC_PLANE_BYTES + k4 * 32) / 16);
                 umma_bf16(acc_main, ah, bh, idesc, (kb >= 3 || k4 > 0) ? 1u : 0u);
                 umma_bf16(acc_cross, ah, bl, idesc, (kb | k4) ? 1u : 0u);
                 umma_bf16(acc_cross, al, bh, idesc, 1u);
