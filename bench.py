@@ -42,9 +42,12 @@ SIMPLE_WORKLOADS = {
 METRIC = "utterances/sec fwd+bwd"
 UNIT = "utt/s"
 
-# DRAM bytes (read + write) of one dense-gradient launch at the c2 workload, from the ncu capture
-# summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until captured.
-NCU_TRAFFIC_PER_LAUNCH = {"c2": None}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from the
+# ncu captures summarised in profiles/: c2 = the lattice launch with its clearing blocks
+# (ctct_loss_c2_kernels.md); c4 = the grad_f GEMM, captured at half the batch (c4s,
+# simple_loss_c4s_kernels.md) and doubled, since traffic is proportional to the number of utterances.
+NCU_TRAFFIC_PER_LAUNCH = {"c2": 10796544 + 1038705000, "c4s": 209618176 + 91585792,
+                          "c4": 2 * (209618176 + 91585792)}
 
 
 def workload_string(name, n_gpus):
@@ -511,20 +514,27 @@ def run_b200_simple(args):
     hbm_peak, hbm_kind = peaks()
     flops = 2.0 * B * T * U1 * V                       # one multiply-add per (t, u, v): the contraction itself
     tc_ach = flops / (k_ms["logmm_tc"] * 1e-3) / 1e12
-    roofline = {"kernel": "k_logmm_tc (tcgen05 GEMM of the max-shifted exponentials, log/max epilogue)",
-                "bound": "tensor", "achieved": tc_ach, "peak": tc_peak, "unit": "TFLOP/s", "frac": tc_ach / tc_peak,
-                "peak_source": f"of {tc_kind} (burst cuBLAS bf16)", "algorithmic_flops": flops,
-                "issued_flops": 3 * flops, "traffic": NCU_TRAFFIC_PER_LAUNCH.get(args.workload),
-                "note": "each product is issued as three bf16 MMAs (hi*hi, hi*lo, lo*hi) for float32-level accuracy; "
-                        "at these shapes the kernel is bound by its operand planes (HBM/L2), not the tensor pipe"}
+    gf_bytes = 4 * (2 * B * T * V) + 4 * B * U1 * V    # f read, grad_f written, Eg planes (hi + lo) read
+    gg_bytes = 4 * (2 * B * U1 * V) + 4 * B * T * V    # g read, grad_g written, Ef planes (hi + lo) read
+    gf_ach = gf_bytes / (k_ms["den_backward_grad_f"] * 1e-3) / 1e9
+    # dominant launch of the step: the tensor-core GEMM that writes grad_f (its interval also holds the
+    # small weight kernel); it is bound by streaming f in and grad_f out, not by the tensor pipe
+    roofline = {"kernel": "k_logmm_bwd_tc (grad_f = Ef * (P Eg): tcgen05 GEMM with exp epilogue) + k_den_weights",
+                "bound": "hbm", "achieved": gf_ach, "peak": hbm_peak, "unit": "GB/s", "frac": gf_ach / hbm_peak,
+                "peak_source": f"of {hbm_kind}", "algorithmic_bytes": gf_bytes,
+                "traffic": NCU_TRAFFIC_PER_LAUNCH.get(args.workload)}
+    tensor = {"kernel": "k_logmm_tc (tcgen05 GEMM of the max-shifted exponentials, log/max epilogue)",
+              "achieved": tc_ach, "peak": tc_peak, "unit": "TFLOP/s", "frac": tc_ach / tc_peak,
+              "peak_source": f"of {tc_kind} (burst cuBLAS bf16)", "algorithmic_flops": flops, "issued_flops": 3 * flops,
+              "note": "each product is issued as three bf16 MMAs (hi*hi, hi*lo, lo*hi) for float32-level accuracy; "
+                      "at these shapes the kernel is bound by its operand planes (HBM/L2), not the tensor pipe"}
     plane_bytes = 2 * 2 * (B * T * V + B * U1 * V)      # bf16 hi+lo planes of both operands, read once
     split_bytes = 4 * (B * T * V + B * U1 * V) + plane_bytes
-    gf_bytes = 4 * (2 * B * T * V + B * T * U1 * 5) + 4 * B * U1 * V     # f read, grad_f written, weights, Eg planes
-    gg_bytes = 4 * (2 * B * U1 * V) + 4 * B * T * V                      # g read, grad_g written, Ef planes
     kernels = {k: {"ms": v} for k, v in k_ms.items()}
     kernels["exp_split"].update({"GB/s": split_bytes / (k_ms["exp_split"] * 1e-3) / 1e9,
                                  "frac": split_bytes / (k_ms["exp_split"] * 1e-3) / 1e9 / hbm_peak})
-    kernels["logmm_tc"].update({"TFLOP/s": tc_ach, "operand_GB/s": plane_bytes / (k_ms["logmm_tc"] * 1e-3) / 1e9})
+    kernels["logmm_tc"].update({"TFLOP/s": tc_ach, "operand_GB/s": plane_bytes / (k_ms["logmm_tc"] * 1e-3) / 1e9,
+                                "tensor_roofline": tensor})
     for key, nbytes in (("den_backward_grad_f", gf_bytes), ("den_backward_grad_g", gg_bytes)):
         kernels[key].update({"GB/s": nbytes / (k_ms[key] * 1e-3) / 1e9, "frac": nbytes / (k_ms[key] * 1e-3) / 1e9 / hbm_peak,
                              "hbm_peak_source": f"of {hbm_kind}"})
@@ -565,7 +575,7 @@ def run_b200_simple(args):
                    "l2": f"inputs larger than L2: f {4 * B * T * V / 1e6:.0f} MB, g {4 * B * U1 * V / 1e6:.0f} MB, "
                          f"their gradients as much again, bf16 planes {plane_bytes / 1e6:.0f} MB (L2 is 126 MB)",
                    "shard_weights": shard_weights(lx_g, ly_g, plan)},
-        "clocks": clocks, "e2e": e2e, "gpu_launches": 10 * args.steps * world,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": 13 * args.steps * world,
         "roofline": roofline, "kernels": kernels, "host_enqueue_us_per_step": host_us,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
