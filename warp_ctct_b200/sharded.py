@@ -12,7 +12,7 @@ from typing import List, Optional, Sequence
 import torch
 import torch.distributed as dist
 
-from . import FusedCTCTLoss, FusedCTCTLossReduced, _as_int, _require_cuda
+from . import FusedCTCTLoss, _as_int, _fused_backward, _fused_forward, _require_cuda
 
 
 def plan_shards(frames_lengths: Sequence[int], labels_lengths: Sequence[int], world_size: int) -> List[List[int]]:
@@ -37,21 +37,43 @@ def shard_weights(frames_lengths, labels_lengths, plan) -> List[int]:
     return [sum(int(frames_lengths[n]) * (int(labels_lengths[n]) + 1) for n in idx) for idx in plan]
 
 
+def _multi_rank(group) -> bool:
+    return dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+
+
 class _AllReduceSum(torch.autograd.Function):
     """y = sum over ranks of x.  Each rank back-propagates only through its own term, so the
     backward is the identity (every rank seeds the same global loss with the same grad)."""
 
     @staticmethod
     def forward(ctx, x: torch.Tensor, group):
-        # in place: the local partial sum is not needed by anything else
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-            dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
-        ctx.mark_dirty(x)
-        return x
+        y = x.clone()
+        if _multi_rank(group):
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+        return y
 
     @staticmethod
     def backward(ctx, grad):
         return grad, None
+
+
+class _ShardedReducedLoss(torch.autograd.Function):
+    """This rank's share of the reduced global loss straight out of the kernels (see
+    FusedCTCTLossReduced), all-reduced in place before autograd ever sees it: one 4-byte
+    collective and no extra kernel.  The backward is local."""
+
+    @staticmethod
+    def forward(ctx, log_probs, labels, lx, ly, requires_grad: bool, mean: bool, average_frames: bool, norm: float,
+                group):
+        loss = _fused_forward(ctx, log_probs, labels, lx, ly, requires_grad, 2 if mean else 1, bool(average_frames),
+                              float(norm))[0]
+        if _multi_rank(group):
+            dist.all_reduce(loss, op=dist.ReduceOp.SUM, group=group)
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_loss):
+        return _fused_backward(ctx, grad_loss), None, None, None, None, None, None, None, None
 
 
 def all_reduce_sum(x: torch.Tensor, group=None) -> torch.Tensor:
@@ -96,10 +118,9 @@ def sharded_ctct_loss(log_probs: torch.Tensor, labels: torch.Tensor, frames_leng
     if reduction in ("mean", "sum") and log_probs.size(0) > 0:
         # this rank's share of the global loss straight out of the kernels (for 'mean' already
         # divided by the global batch); the all-reduce of that one float completes it
-        part = FusedCTCTLossReduced.apply(log_probs, _as_int(labels), _as_int(frames_lengths),
-                                          _as_int(labels_lengths), enable_grad, reduction == "mean",
-                                          bool(average_frames), float(global_batch))
-        return part if world == 1 else all_reduce_sum(part, group)
+        return _ShardedReducedLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
+                                         enable_grad, reduction == "mean", bool(average_frames), float(global_batch),
+                                         group)
     costs = FusedCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
                                 enable_grad)
     return reduce_costs(costs, frames_lengths, global_batch, reduction, average_frames, group)
