@@ -58,6 +58,9 @@ size_t ctct_b200_workspace_bytes(int64_t N, int64_t T, int64_t U1, int want_grad
  *         log-probs per (n,t,u), one 16-byte record {g0,g1,g2,0} each
  * Labels are only dereferenced for u < ly[n]; frames t >= lx[n] and contexts
  * u > ly[n] of log_probs are never read.
+  *   log_probs may also point to pinned (page-locked, device-accessible) HOST memory: the gather
+ *   kernel is the only reader and fetches just the three elements it needs per row over PCIe.
+ *   Every other pointer must be device memory.
  */
 int ctct_b200_loss_forward(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx,
                            const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,

@@ -395,3 +395,26 @@ def test_benchmark_shape_properties(W):
         got = grad[n].cpu().numpy()
         assert np.abs(got - d64[0]).max() < 2e-5
         assert np.abs(got - d[0]).max() < 1e-4 + np.abs(d[0] - d64[0]).max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("reduction,average_frames", [("mean", False), ("sum", True), ("none", True)])
+def test_loss_and_grad_reads_a_pinned_host_joint_tensor(W, dtype, reduction, average_frames):
+    """ctct_loss_and_grad with the joint tensor left in pinned host memory (the gather kernel reads
+    it in place) must give exactly what the autograd path gives on a device copy."""
+    lp, ys, lx, ly = make_case(3, 70, 40, 600, sigma=1.5, seed=31, lx_range=(30, 70), ly_range=(5, 39), cap_half=True)
+    lp_host = torch.from_numpy(lp).to(dtype).pin_memory()
+    ys_h, lx_h, ly_h = (torch.from_numpy(a) for a in (ys, lx, ly))
+    loss_h, grad_h = W.ctct_loss_and_grad(lp_host, ys_h, lx_h, ly_h, reduction=reduction, average_frames=average_frames,
+                                          device=DEV)
+    assert grad_h.is_cuda and grad_h.dtype == dtype and grad_h.shape == lp_host.shape
+    x = lp_host.to(DEV).requires_grad_(True)
+    loss_d = W.ctct_loss(x, ys_h.to(DEV), lx_h.to(DEV), ly_h.to(DEV), reduction=reduction, average_frames=average_frames)
+    loss_d.sum().backward()
+    assert torch.equal(loss_h, loss_d.detach())
+    assert torch.equal(grad_h, x.grad)
+    # and the same call on the device copy
+    loss_c, grad_c = W.ctct_loss_and_grad(x.detach(), ys_h, lx_h, ly_h, reduction=reduction, average_frames=average_frames)
+    assert torch.equal(loss_c, loss_h) and torch.equal(grad_c, grad_h)
+    with pytest.raises(RuntimeError):
+        W.ctct_loss_and_grad(torch.from_numpy(lp), ys_h, lx_h, ly_h)   # pageable host memory

@@ -17,7 +17,7 @@ import torch
 from . import _lib
 
 __version__ = "0.3.0"  # the reference release whose API this mirrors (setup.py:18)
-__all__ = ["ctct_loss", "ctct_simple_loss"]
+__all__ = ["ctct_loss", "ctct_simple_loss", "ctct_loss_and_grad"]
 
 T = torch.Tensor
 
@@ -62,12 +62,13 @@ def _sizes(N: int, Tm: int, U1: int, want_grad: bool):
 
 
 def _fused_forward(ctx, log_probs: T, labels: T, lx: T, ly: T, requires_grad: bool, red: int, average_frames: bool,
-                   norm: float):
+                   norm: float, device: Optional[torch.device] = None):
     """Shared forward of the two fused autograd functions: one C-ABI call (gather, lattice with the
     gradient buffer cleared on the side, occupancy gradient, optional reduction).
-    Returns the float32 tensor [loss, costs[0..N)]."""
+    Returns the float32 tensor [loss, costs[0..N)].  `device` is where everything but `log_probs`
+    lives when `log_probs` itself is pinned host memory that the gather kernel reads in place."""
     N, Tm, U1, V = log_probs.shape
-    dev = log_probs.device
+    dev = log_probs.device if device is None else device
     lib = _lib.lib()
     g3_bytes, ws_bytes = _sizes(N, Tm, U1, requires_grad)
     switch = torch.cuda.current_device() != dev.index
@@ -271,6 +272,61 @@ def ctct_loss(log_probs: torch.FloatTensor,
     costs = FusedCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
                                 enable_grad)
     return _reduce(costs, frames_lengths, reduction, average_frames)
+
+
+class _Saved:
+    """Stand-in for an autograd context when forward and backward run back to back."""
+
+    def save_for_backward(self, *tensors):
+        self.saved_tensors = tensors
+
+
+def ctct_loss_and_grad(log_probs: T, labels: T, frames_lengths: T, labels_lengths: T,
+                       reduction: Optional[str] = "mean", average_frames: bool = False,
+                       device: Optional[torch.device] = None, global_batch: Optional[int] = None):
+    """Loss and its dense gradient d loss / d log_probs in one call (no counterpart in the reference,
+    which always goes through autograd): for a loss that ends the graph, `loss.backward()` seeds 1.0,
+    so both passes can run back to back.
+
+    `log_probs` may live in PINNED HOST memory (e.g. a joint tensor that was off-loaded, or produced
+    on the host): the gather kernel then reads the three log-probs it needs per (n, t, u) row in
+    place over PCIe (about 100 bytes per row instead of V * sizeof), and nothing else touches the
+    tensor.  Labels and lengths may be host tensors too (copied; they are tiny).  Loss and gradient
+    are created on `device` (default: the device of `log_probs`, or the current CUDA device).
+
+    Returns (loss, grad): `loss` as `ctct_loss` returns it, `grad` (N,T,U,V) in the dtype of
+    `log_probs`; with reduction 'none' the gradient is that of `costs.sum()`.  `global_batch`
+    replaces N as the divisor of 'mean' (for a shard of a larger batch)."""
+    assert reduction is None or reduction in ("none", "mean", "sum")
+    assert log_probs.dim() == 4 and labels.dim() == 2
+    assert log_probs.size(2) == labels.size(1) + 1
+    assert log_probs.size(0) == labels.size(0) == frames_lengths.size(0) == labels_lengths.size(0)
+    if log_probs.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise RuntimeError("log_probs must be float32, float16 or bfloat16")
+    if not log_probs.is_contiguous():
+        raise RuntimeError("log_probs must be contiguous")
+    if log_probs.is_cuda:
+        dev = log_probs.device
+    else:
+        if not log_probs.is_pinned():
+            raise RuntimeError("a host log_probs tensor must be in pinned memory (tensor.pin_memory())")
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ys, lx, ly = (_as_int(t).to(dev, non_blocking=True) for t in (labels, frames_lengths, labels_lengths))
+    N = log_probs.size(0)
+    norm = float(N if global_batch is None else global_batch)
+    red = {"mean": 2, "sum": 1}.get(reduction, 0)
+    ctx = _Saved()
+    out = _fused_forward(ctx, log_probs, ys, lx, ly, True, red, bool(average_frames) and red != 0, norm, device=dev)
+    if red:
+        seed = torch.ones((), dtype=torch.float32, device=dev)
+        loss = out[0]
+    else:
+        seed = torch.ones((N,), dtype=torch.float32, device=dev)
+        loss = out[1:]
+        if average_frames:
+            loss = loss / lx
+            seed = seed / lx
+    return loss, _fused_backward(ctx, seed)
 
 
 from .simple import (FusedSimpleCTCTLoss, LogMMExp, SimpleCTCTLoss, ctct_loss_simple_fwd,  # noqa: E402,F401
