@@ -17,7 +17,7 @@ import torch
 from . import _lib
 
 __version__ = "0.3.0"  # the reference release whose API this mirrors (setup.py:18)
-__all__ = ["ctct_loss", "ctct_simple_loss", "ctct_loss_and_grad"]
+__all__ = ["ctct_loss", "ctct_simple_loss"]  # as the reference; ctct_loss_and_grad is an extra
 
 T = torch.Tensor
 
