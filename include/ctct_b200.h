@@ -276,6 +276,17 @@ int ctct_b200_simple_backward_tc(const float *grads3, const float *grad_out, con
                                  void *tc_workspace, size_t tc_workspace_bytes, void *stream);
 
 /*
+ * log_matmul_backward (csrc/binding.cpp:247-324) as two tensor-core GEMMs, for a result that
+ * ctct_b200_log_matmul_tc computed: lhs (B,M,K), rhsT (B,N,K), res (B,M,N) are that call's f, g and
+ * den, tc_workspace its untouched workspace; grad_out (B,M,N) contiguous float32, any sign.
+ * grad_lhs (B,M,K) and grad_rhsT (B,N,K) are written once each; either may be NULL.  Falls back to
+ * the exact kernel inside the same call when the forward call had to (flag in the workspace).
+ */
+int ctct_b200_log_matmul_backward_tc(const float *grad_out, const float *lhs, const float *rhsT, const float *res,
+                                     int64_t B, int64_t M, int64_t K, int64_t N, float *grad_lhs, float *grad_rhsT,
+                                     void *tc_workspace, size_t tc_workspace_bytes, void *stream);
+
+/*
  * Optional per-kernel timing for benchmarks (no counterpart in the reference).  While
  * enabled, every ctct_b200_loss_forward records CUDA events on its stream before the gather,
  * after the gather, after the lattice and after the occupancy-gradient kernel, and every

@@ -45,6 +45,7 @@ SIGNATURES = {
     "ctct_b200_log_matmul_tc_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64]),
     "ctct_b200_log_matmul_tc": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _sz, _vp]),
     "ctct_b200_log_matmul_backward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
+    "ctct_b200_log_matmul_backward_tc": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),
     "ctct_b200_simple_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
     "ctct_b200_simple_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
     "ctct_b200_simple_backward_tc": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp,

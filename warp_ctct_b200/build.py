@@ -41,7 +41,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not is_stale():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-o", LIB, *[os.path.join(CSRC, s) for s in SOURCES]]
+    tmp = LIB + ".partial"  # the library appears under its name only when it is complete
+    cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-o", tmp, *[os.path.join(CSRC, s) for s in SOURCES]]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -50,7 +51,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         print(res.stdout + res.stderr)
     if res.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    os.replace(tmp, LIB)
     return LIB
 
 

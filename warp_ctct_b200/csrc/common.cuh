@@ -70,6 +70,24 @@ __device__ __forceinline__ float load_sparse(const __nv_bfloat16 *p) {
     return __bfloat162float(__ushort_as_bfloat16(v));
 }
 
+// The same reads without a fill-size hint: for a source in pinned host memory, where every
+// byte asked for crosses PCIe.
+__device__ __forceinline__ float load_remote(const float *p) {
+    float v;
+    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float load_remote(const __half *p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return __half2float(__ushort_as_half(v));
+}
+__device__ __forceinline__ float load_remote(const __nv_bfloat16 *p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return __bfloat162float(__ushort_as_bfloat16(v));
+}
+
 __host__ __device__ __forceinline__ int64_t pad4(int64_t x) { return (x + 3) & ~int64_t(3); }
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {

@@ -122,12 +122,14 @@ unsigned clear_blocks(const ClearSlice &c) {
 // clearing they host), clearing beside the lattice is free (the lattice is bound by its own
 // dependent instruction stream).  So the lattice launch takes everything; the split stays
 // parametric.  Slices are whole chunks, the last one takes the remainder and the tail.
-void plan_clear(void *clear, size_t bytes, ClearSlice out[3]) {
+// all_in_gather: the joint tensor sits in pinned host memory, so the gather launch lasts as long
+// as PCIe takes and hides the whole clearing.
+void plan_clear(void *clear, size_t bytes, ClearSlice out[3], bool all_in_gather = false) {
     out[0] = out[1] = out[2] = kNoClear;
     if (!clear || !bytes) return;
     const unsigned long long vecs = bytes / 16;
     const unsigned long long chunks = (vecs + CLEAR_CHUNK - 1) / CLEAR_CHUNK;
-    const unsigned long long c0 = 0, c2 = 0;
+    const unsigned long long c0 = all_in_gather ? chunks : 0, c2 = 0;
     const unsigned long long c1 = chunks - c0 - c2;
     uint4 *p = static_cast<uint4 *>(clear);
     unsigned long long done = 0;
@@ -191,11 +193,20 @@ int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st, Cle
     return CTCT_ERR_UNSUPPORTED;
 }
 
+bool is_pinned_host(const void *p) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) == cudaSuccess) return attr.type == cudaMemoryTypeHost;
+    cudaGetLastError();
+    return false;
+}
+
 template <typename InT>
 int launch_gather_t(const void *lp, const int *ys, const int *lx, const int *ly, float *out, int64_t N,
                     int64_t T, int64_t U1, int64_t V, bool internal, int valid_only, cudaStream_t st, ClearSlice clear) {
     const int64_t total = internal ? N * T * U1 * 4 : N * T * U1 * 3;
     if (total == 0) return CTCT_OK;
+    // a joint tensor in pinned host memory is read in place: no fill-size hint on those loads
+    if (is_pinned_host(lp)) valid_only |= 2;
     const int64_t want = (total + 256 * 4 - 1) / (256 * 4);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
     const int own = static_cast<int>(want < cap ? want : cap);
@@ -460,7 +471,7 @@ int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int3
 
     if (clear && reinterpret_cast<uintptr_t>(clear) % 16) return CTCT_ERR_ARG;
     ClearSlice cs[3];
-    plan_clear(want_grad ? clear : nullptr, clear_bytes, cs);
+    plan_clear(want_grad ? clear : nullptr, clear_bytes, cs, is_pinned_host(log_probs));
     if (!want_grad && clear && clear_bytes) cs[1] = ClearSlice{static_cast<uint4 *>(clear), clear_bytes / 16, static_cast<int>(clear_bytes % 16), 0};
     cudaEvent_t *slot = prof_slot(0);
     prof_mark(slot, 0, st);
@@ -830,7 +841,7 @@ int ctct_b200_simple_forward(const float *f, const float *g, const float *den, c
 constexpr int BW_F_STAGES = 2, BW_F_EBUFS = 3, BW_G_STAGES = 4, BW_G_EBUFS = 1;
 // grad_f with U+1 <= 128: the weight tile stays in shared memory (64 KB), only Eg streams (16 KB stages)
 constexpr int BW_R_STAGES = 4, BW_R_EBUFS = 3;
-static int den_backward_tc(const float4 *g4, const float *grad_out, const float *f, const float *g, const float *den,
+static int den_backward_tc(const float4 *g4, const float *gout, const float *grad_out, const float *f, const float *g, const float *den,
                            const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
                            float *grad_f, float *grad_g, char *ws, const TcLayout &l, cudaEvent_t *slot,
                            cudaStream_t st) {
@@ -842,6 +853,7 @@ static int den_backward_tc(const float4 *g4, const float *grad_out, const float 
     DenWeightArgs w;
     w.grads3 = g4;
     w.scale = grad_out;
+    w.gout = gout;
     w.den = den;
     w.mf = mf;
     w.mg = mg;
@@ -935,7 +947,7 @@ static int simple_backward_impl(const float *grads3, const float *grad_out, cons
             if (reinterpret_cast<uintptr_t>(f) % 16 || reinterpret_cast<uintptr_t>(g) % 16 ||
                 (grad_f && reinterpret_cast<uintptr_t>(grad_f) % 16) || (grad_g && reinterpret_cast<uintptr_t>(grad_g) % 16))
                 return CTCT_ERR_ARG;
-            int rc = den_backward_tc(g4, grad_out, f, g, den, lx, ly, N, T, U1, V, grad_f, grad_g,
+            int rc = den_backward_tc(g4, nullptr, grad_out, f, g, den, lx, ly, N, T, U1, V, grad_f, grad_g,
                                      static_cast<char *>(tc_ws), l, slot, st);
             if (rc) return rc;
             run_flags = reinterpret_cast<const int *>(static_cast<char *>(tc_ws) + l.flags);
@@ -989,6 +1001,33 @@ static int simple_backward_impl(const float *grads3, const float *grad_out, cons
     }
     prof_mark(slot, 3, st);
     return CTCT_OK;
+}
+
+int ctct_b200_log_matmul_backward_tc(const float *grad_out, const float *lhs, const float *rhsT, const float *res,
+                                     int64_t B, int64_t M, int64_t K, int64_t N, float *grad_lhs, float *grad_rhsT,
+                                     void *tc_workspace, size_t tc_workspace_bytes, void *stream) {
+    if (!tc_shape_ok(B, M, N, K)) return CTCT_ERR_UNSUPPORTED;
+    if (!grad_out || !lhs || !rhsT || !res || !tc_workspace) return CTCT_ERR_ARG;
+    if (!grad_lhs && !grad_rhsT) return CTCT_OK;
+    const TcLayout l = tc_layout(B, M, N, K);
+    if (tc_workspace_bytes < l.total || reinterpret_cast<uintptr_t>(tc_workspace) % 256) return CTCT_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = den_backward_tc(nullptr, grad_out, nullptr, lhs, rhsT, res, nullptr, nullptr, B, M, N, K, grad_lhs, grad_rhsT,
+                             static_cast<char *>(tc_workspace), l, nullptr, st);
+    if (rc) return rc;
+    // exact kernel: a no-op unless a flag in the workspace says the tensor-core result cannot be used
+    LogmmBwdArgs a = {};
+    a.lhs = lhs;
+    a.rhsT = rhsT;
+    a.res = res;
+    a.gout = grad_out;
+    a.grad_lhs = grad_lhs;
+    a.grad_rhsT = grad_rhsT;
+    a.M = (int)M;
+    a.Nc = (int)N;
+    a.K = (int)K;
+    a.run_flags = reinterpret_cast<const int *>(static_cast<char *>(tc_workspace) + l.flags);
+    return launch_logmm_bwd(a, B, st);
 }
 
 int ctct_b200_simple_backward(const float *grads3, const float *grad_out, const float *f, const float *g,

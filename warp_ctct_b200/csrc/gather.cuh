@@ -20,9 +20,11 @@ template <typename InT, typename IdxT, bool INTERNAL>
 __global__ void __launch_bounds__(256)
 k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__restrict__ lx,
           const int *__restrict__ ly, float *__restrict__ out, int T, int U1, int V,
-          IdxT total, int valid_only, const ClearSlice clear) {
+          IdxT total, int mode, const ClearSlice clear) {
     if (clear_role(clear, nullptr, 0)) return;
     constexpr int PER = 4;
+    const int valid_only = mode & 1;    // read only frames t < lx[n] and contexts u <= ly[n]
+    const bool remote = (mode & 2) != 0;  // lp is pinned host memory
     const IdxT stride = static_cast<IdxT>(clear.ptr ? clear.first_block : gridDim.x) * blockDim.x;
     IdxT e0 = static_cast<IdxT>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int U = U1 - 1;
@@ -58,7 +60,7 @@ k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__r
                     if (k == 2 && u < U && (!valid_only || u < ly[n])) idx = ys[static_cast<int64_t>(n) * U + u];
                     idx = min(max(idx, 0), V - 1);
                     const int64_t row = static_cast<int64_t>(nt) * U1 + u;
-                    const float x = load_sparse(lp + row * V + idx);
+                    const float x = remote ? load_remote(lp + row * V + idx) : load_sparse(lp + row * V + idx);
                     val[j] = INTERNAL ? to_log2(x) : x;
                 }
             }

@@ -44,6 +44,7 @@ constexpr int bw_smem_bytes(int stages, int ebufs, bool a_res) {
 struct DenWeightArgs {
     const float4 *grads3;  // [B][T][U1] records {g0,g1,g2,0}; w = -scale[b] * (g0+g1+g2)
     const float *scale;    // [B]
+    const float *gout;     // or: w given directly, (B,T,U1), any sign, every entry valid (then lx, ly unused)
     const float *den;      // (B,T,U1)
     const float *mf;       // (B,T)
     const float *mg;       // (B,U1)
@@ -58,15 +59,20 @@ __global__ void __launch_bounds__(128) k_den_weights(const DenWeightArgs a) {
     if (a.flags[0] | a.flags[1]) return;
     const int64_t bt = blockIdx.x;
     const int b = static_cast<int>(bt / a.T), t = static_cast<int>(bt - static_cast<int64_t>(b) * a.T);
-    const bool row_ok = t < a.lx[b];
-    const int un = min(a.ly[b] + 1, a.U1);
-    const float sc = -a.scale[b];
+    const bool row_ok = a.gout ? true : t < a.lx[b];
+    const int un = a.gout ? a.U1 : min(a.ly[b] + 1, a.U1);
+    const float sc = a.gout ? 0.0f : -a.scale[b];
     const float mfr = a.mf[bt];
     for (int u = threadIdx.x; u < a.U1p; u += blockDim.x) {
         float p = 0.0f;
         if (row_ok && u < un) {
-            const float4 g3 = a.grads3[bt * a.U1 + u];
-            const float w = sc * (g3.x + g3.y + g3.z);
+            float w;
+            if (a.gout) {
+                w = a.gout[bt * a.U1 + u];
+            } else {
+                const float4 g3 = a.grads3[bt * a.U1 + u];
+                w = sc * (g3.x + g3.y + g3.z);
+            }
             if (w != 0.0f) p = w * ex2((mfr + a.mg[static_cast<int64_t>(b) * a.U1 + u] - a.den[bt * a.U1 + u]) * LOG2E);
         }
         const __nv_bfloat16 h = __float2bfloat16_rn(p);

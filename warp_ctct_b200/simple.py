@@ -94,22 +94,58 @@ def log_matmul_backward(grad_out: Optional[T], lhs: T, rhs: T, res: T, grad_mask
     return grad_lhs, (grad_rhs_t.transpose(1, 2) if grad_rhs_t is not None else None)
 
 
+def _tc_operands(lhs: T, rhs: T):
+    """(f, g) = (lhs, rhs^T) when they are what the tensor-core kernels take: float32 CUDA tensors,
+    lhs (B,M,K) contiguous and rhs (B,K,N) a transposed view of a contiguous (B,N,K) tensor (what
+    warp_ctct/__init__.py:199 passes), 16-byte aligned, K % 8 == 0, K >= 64; else None."""
+    if not (lhs.is_cuda and rhs.is_cuda and lhs.dtype == torch.float32 and rhs.dtype == torch.float32):
+        return None
+    if lhs.dim() != 3 or rhs.dim() != 3 or lhs.size(0) != rhs.size(0) or lhs.size(2) != rhs.size(1):
+        return None
+    g = rhs.transpose(1, 2)
+    if not (lhs.is_contiguous() and g.is_contiguous()) or lhs.data_ptr() % 16 or g.data_ptr() % 16:
+        return None
+    B, M, K = lhs.shape
+    if _lib.lib().ctct_b200_log_matmul_tc_workspace_bytes(B, M, g.size(1), K) == 0:
+        return None
+    return lhs, g
+
+
 class LogMMExp(torch.autograd.Function):
-    """log(exp(lhs) @ exp(rhs)) with its analytic backward (warp_ctct/__init__.py:36-52)."""
+    """log(exp(lhs) @ exp(rhs)) with its analytic backward (warp_ctct/__init__.py:36-52).  Runs on
+    the tensor cores, forward and backward, when the operands allow it (see _tc_operands)."""
 
     @staticmethod
     def forward(ctx: Any, lhs: T, rhs: T, track_l: bool = True, track_r: bool = True) -> T:
-        mm = log_matmul(lhs, rhs)
+        ops = _tc_operands(lhs, rhs)
+        if ops is not None:
+            mm, ws = log_matmul_tc(ops[0], ops[1], keep_workspace=True)
+        else:
+            mm, ws = log_matmul(lhs, rhs), None
         if track_l or track_r:
-            ctx.save_for_backward(lhs, rhs, mm)
+            ctx.save_for_backward(lhs, rhs, mm, ws if ws is not None else lhs.new_empty(0))
             ctx.track = [track_l, track_r]
         return mm
 
     @staticmethod
     def backward(ctx: Any, grad_outputs: T) -> Any:
-        lhs, rhs, res = ctx.saved_tensors
-        grad_lhs, grad_rhs = log_matmul_backward(grad_outputs, lhs, rhs, res, ctx.track)
-        return grad_lhs, grad_rhs, None, None
+        lhs, rhs, res, ws = ctx.saved_tensors
+        if ws.numel() == 0:
+            grad_lhs, grad_rhs = log_matmul_backward(grad_outputs, lhs, rhs, res, ctx.track)
+            return grad_lhs, grad_rhs, None, None
+        B, M, K = lhs.shape
+        g = rhs.transpose(1, 2)  # contiguous (B,N,K)
+        N = g.size(1)
+        dev = lhs.device
+        go = grad_outputs.to(torch.float32).contiguous()
+        grad_lhs = torch.empty((B, M, K), dtype=torch.float32, device=dev) if ctx.track[0] else None
+        grad_g = torch.empty((B, N, K), dtype=torch.float32, device=dev) if ctx.track[1] else None
+        with torch.cuda.device(dev):
+            rc = _lib.lib().ctct_b200_log_matmul_backward_tc(
+                _lib.ptr(go), _lib.ptr(lhs), _lib.ptr(g), _lib.ptr(res), B, M, K, N, _lib.ptr(grad_lhs), _lib.ptr(grad_g),
+                _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+        _lib.check(rc, "ctct_b200_log_matmul_backward_tc")
+        return grad_lhs, (grad_g.transpose(1, 2) if grad_g is not None else None), None, None
 
 
 # --------------------------------------------------------------------------------------------
