@@ -418,3 +418,34 @@ def test_loss_and_grad_reads_a_pinned_host_joint_tensor(W, dtype, reduction, ave
     assert torch.equal(loss_c, loss_h) and torch.equal(grad_c, grad_h)
     with pytest.raises(RuntimeError):
         W.ctct_loss_and_grad(torch.from_numpy(lp), ys_h, lx_h, ly_h)   # pageable host memory
+
+
+def test_forward_and_backward_replay_from_a_cuda_graph(W):
+    """The C ABI neither allocates nor synchronises, so a whole step (ctct_loss forward + backward)
+    can be captured once and replayed: the replay on new input values matches an eager step."""
+    lp, ys, lx, ly = make_case(4, 64, 17, 512, sigma=1.5, seed=41, lx_range=(30, 64), ly_range=(3, 16), cap_half=True)
+    lp2 = make_case(4, 64, 17, 512, sigma=1.0, seed=42)[0]
+    ys_t, lx_t, ly_t = _dev(ys, lx, ly)
+    static_lp = torch.from_numpy(lp).to(DEV).requires_grad_(True)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):          # warm-up outside the capture (lazy initialisation, allocator pools)
+        for _ in range(2):
+            static_lp.grad = None
+            W.ctct_loss(static_lp, ys_t, lx_t, ly_t, reduction="mean").backward()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    static_lp.grad = None
+    with torch.cuda.graph(graph):
+        static_loss = W.ctct_loss(static_lp, ys_t, lx_t, ly_t, reduction="mean")
+        static_loss.backward()
+    for values in (lp2, lp):
+        with torch.no_grad():
+            static_lp.copy_(torch.from_numpy(values).to(DEV))
+        graph.replay()
+        torch.cuda.synchronize()
+        eager = torch.from_numpy(values).to(DEV).requires_grad_(True)
+        loss = W.ctct_loss(eager, ys_t, lx_t, ly_t, reduction="mean")
+        loss.backward()
+        assert torch.equal(static_loss.detach(), loss.detach())
+        assert torch.equal(static_lp.grad, eager.grad)
