@@ -316,6 +316,41 @@ def run_b200(args):
                               "note": "alpha and beta CTAs of all utterances run concurrently; rows = longest utterance"}
         kernels["dense_grad"] = {"ms": k_ms["dense_grad"], "GB/s": ach, "frac": ach / peak}
 
+    # ---- the same step captured once in a CUDA graph and replayed (single GPU; informational) ----
+    graph_ms = None
+    if world == 1:
+        try:
+            # a fresh leaf over the same memory: its gradient accumulator must belong to the capturing stream
+            lp_g = lp.detach().requires_grad_(True)
+
+            def graph_step():
+                sharded_ctct_loss(lp_g, ys_t, lx_t, ly_t, global_batch=G, reduction="mean").backward()
+
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    lp_g.grad = None
+                    graph_step()
+            torch.cuda.current_stream().wait_stream(side)
+            lp_g.grad = None
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                graph_step()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize(dev)
+            ev0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            ev1.record()
+            torch.cuda.synchronize(dev)
+            graph_ms = ev0.elapsed_time(ev1) / args.steps
+            del graph, lp_g
+        except Exception as exc:  # capture is an extra: report why it did not happen
+            graph_ms = f"not captured: {exc}"
+        lp.grad = None
+
     # ---- end to end through the public API, inputs in pinned host memory ----
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     lp_host = torch.empty((B, T, U1, V), dtype=tdt, pin_memory=True)
@@ -379,6 +414,8 @@ def run_b200(args):
         "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps * world,
         "roofline": roofline, "kernels": kernels, "host_enqueue_us_per_step": host_us,
     }
+    if graph_ms is not None:
+        line["cuda_graph_replay_ms_per_step"] = graph_ms
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle
