@@ -88,6 +88,14 @@ __device__ __forceinline__ float load_remote(const __nv_bfloat16 *p) {
     return __bfloat162float(__ushort_as_bfloat16(v));
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may
+// start while the kernel before it in the stream is still running; pdl_wait() returns once that
+// kernel has completed and its writes are visible (at once when nothing is pending, or when the
+// launch did not carry the attribute).  pdl_trigger() lets the NEXT kernel in the stream start
+// launching once every block of this one has called it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __host__ __device__ __forceinline__ int64_t pad4(int64_t x) { return (x + 3) & ~int64_t(3); }
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {

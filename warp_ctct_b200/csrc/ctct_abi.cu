@@ -48,6 +48,23 @@ inline void prof_mark(cudaEvent_t *slot, int i, cudaStream_t st) {
     if (slot) cudaEventRecord(slot[i], st);
 }
 
+// Launch with programmatic stream serialisation: the kernel may be set up, and start, while the
+// kernel before it in the stream drains; it must call pdl_wait() before touching that kernel's output.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 int sm_count() {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -154,7 +171,7 @@ int launch_lattice_inst(const LatticeArgs &a, unsigned grid, int block, size_t s
                                  static_cast<int>(smem)) != cudaSuccess)
             return check_launch("lattice smem attribute");
     }
-    k_lattice<C, MAXT, MINB><<<grid, block, smem, st>>>(a);
+    launch_pdl(k_lattice<C, MAXT, MINB>, dim3(grid), dim3(block), smem, st, a);
     return check_launch("lattice");
 }
 
@@ -208,7 +225,9 @@ int launch_gather_t(const void *lp, const int *ys, const int *lx, const int *ly,
     // a joint tensor in pinned host memory is read in place: no fill-size hint on those loads
     if (is_pinned_host(lp)) valid_only |= 2;
     const int64_t want = (total + 256 * 4 - 1) / (256 * 4);
-    const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+    // at most one resident wave (8 blocks of 256 threads per SM): every block starts at once, so the
+    // launch behind this one is released as early as possible
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     const int own = static_cast<int>(want < cap ? want : cap);
     clear.first_block = static_cast<unsigned>(own);
     const unsigned grid = static_cast<unsigned>(own) + clear_blocks(clear);
@@ -216,14 +235,14 @@ int launch_gather_t(const void *lp, const int *ys, const int *lx, const int *ly,
     const bool small = total < (int64_t(1) << 31) - int64_t(own) * 256 * 4;
     if (internal) {
         if (small)
-            k_gather3<InT, unsigned, true><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only, clear);
+            launch_pdl(k_gather3<InT, unsigned, true>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only, clear);
         else
-            k_gather3<InT, unsigned long long, true><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only, clear);
+            launch_pdl(k_gather3<InT, unsigned long long, true>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only, clear);
     } else {
         if (small)
-            k_gather3<InT, unsigned, false><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only, clear);
+            launch_pdl(k_gather3<InT, unsigned, false>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only, clear);
         else
-            k_gather3<InT, unsigned long long, false><<<grid, 256, 0, st>>>(p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only, clear);
+            launch_pdl(k_gather3<InT, unsigned long long, false>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only, clear);
     }
     return check_launch("gather");
 }
@@ -272,7 +291,7 @@ int launch_fill_grad(const WsLayout &w, char *ws, const int *ys, const int *lx, 
     if (own + clear_blocks(clear) > 0x7fffffffull) return CTCT_ERR_UNSUPPORTED;
     clear.first_block = static_cast<unsigned>(own);
     g.clear = clear;
-    k_fill_grad<<<static_cast<unsigned>(own) + clear_blocks(clear), 256, 0, st>>>(g);
+    launch_pdl(k_fill_grad, dim3(static_cast<unsigned>(own) + clear_blocks(clear)), dim3(256), 0, st, g);
     return check_launch("fill_grad");
 }
 
@@ -425,9 +444,9 @@ int launch_patch_t(const DenseArgs &a, int64_t N, cudaStream_t st) {
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
     const bool sectors = (static_cast<int64_t>(a.V) * sizeof(OutT)) % 32 == 0 && reinterpret_cast<uintptr_t>(a.out) % 32 == 0;
     if (sectors)
-        k_dense_patch<OutT, true><<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(a, rows);
+        launch_pdl(k_dense_patch<OutT, true>, dim3(static_cast<unsigned>(want < cap ? want : cap)), dim3(256), 0, st, a, rows);
     else
-        k_dense_patch<OutT, false><<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(a, rows);
+        launch_pdl(k_dense_patch<OutT, false>, dim3(static_cast<unsigned>(want < cap ? want : cap)), dim3(256), 0, st, a, rows);
     return check_launch("dense_patch");
 }
 

@@ -21,6 +21,10 @@ __global__ void __launch_bounds__(256)
 k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__restrict__ lx,
           const int *__restrict__ ly, float *__restrict__ out, int T, int U1, int V,
           IdxT total, int mode, const ClearSlice clear) {
+    // everything before this launch is done before anything here runs; from then on the next launch
+    // (the lattice with its clearing blocks) may move in beside this one
+    pdl_wait();
+    pdl_trigger();
     if (clear_role(clear, nullptr, 0)) return;
     constexpr int PER = 4;
     const int valid_only = mode & 1;    // read only frames t < lx[n] and contexts u <= ly[n]

@@ -112,6 +112,7 @@ struct GradArgs {
 // exact 0 because one of the two variables is "impossible" there, so the reference's band
 // guards (gather.cu:335-337,355-359) need no restating.
 __global__ void __launch_bounds__(256) k_fill_grad(const GradArgs a) {
+    pdl_wait();
     if (clear_role(a.clear, nullptr, 0)) return;
     if (a.loss_out != nullptr && blockIdx.x == 0) reduce_costs_block(a.costs, a.lx, a.N, a.red, a.loss_out);
     const int n = blockIdx.x / a.blocks_per_utt;
@@ -367,6 +368,7 @@ __device__ __forceinline__ void write_sector(OutT *row, int sector, const RowPat
 // 32-byte boundaries and V is a multiple of the sector width.
 template <typename OutT, bool SECTORS>
 __global__ void __launch_bounds__(256) k_dense_patch(const DenseArgs a, int64_t rows) {
+    pdl_wait();
     constexpr int ES = 2 * OutOps<OutT>::E;  // elements per 32-byte sector
     const int U = a.U1 - 1, V = a.V;
     for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < rows;

@@ -367,8 +367,10 @@ __device__ __forceinline__ void lattice_run(const LatticeArgs &a, float4 *smem4)
 template <int C, int MAXT, int MINB>
 __global__ void __launch_bounds__(MAXT, MINB) k_lattice(const LatticeArgs a) {
     extern __shared__ __align__(16) float4 smem4[];
+    // clearing blocks need nothing from the gather launch before this one and may run beside it
     if (clear_role(a.clear, smem4, a.smem_bytes)) return;
     if (static_cast<int>(threadIdx.x) >= a.threads) return;
+    pdl_wait();  // the gathered log-probs are complete and visible
     const int dir = a.beta_only ? 1 : static_cast<int>(blockIdx.x & 1);
     const bool multi = a.threads > 32;
     if (dir == 0) {
