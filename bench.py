@@ -617,6 +617,39 @@ def run_b200_simple(args):
                              "hbm_peak_source": f"of {hbm_kind}"})
     kernels["sum_ms"] = sum(k_ms.values())
 
+    # ---- the same step captured once in a CUDA graph and replayed (single GPU; informational) ----
+    graph_ms = None
+    if world == 1:
+        try:
+            f_g, g_g = f.detach().requires_grad_(True), g.detach().requires_grad_(True)
+
+            def graph_step():
+                sharded_ctct_simple_loss(f_g, g_g, ys_t, lx_t, ly_t, global_batch=G, reduction="mean").backward()
+
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    f_g.grad = g_g.grad = None
+                    graph_step()
+            torch.cuda.current_stream().wait_stream(side)
+            f_g.grad = g_g.grad = None
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                graph_step()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize(dev)
+            ev0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            ev1.record()
+            torch.cuda.synchronize(dev)
+            graph_ms = ev0.elapsed_time(ev1) / args.steps
+            del graph, f_g, g_g
+        except Exception as exc:  # capture is an extra: report why it did not happen
+            graph_ms = f"not captured: {exc}"
+
     # ---- end to end: f and g copied from pinned host memory each step, loss read back ----
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
 
@@ -656,6 +689,8 @@ def run_b200_simple(args):
         "roofline": roofline, "kernels": kernels, "host_enqueue_us_per_step": host_us,
         "profiled_pass_ms_per_step": ms_profiled / args.steps,
     }
+    if graph_ms is not None:
+        line["cuda_graph_replay_ms_per_step"] = graph_ms
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle
         cores = oracle.max_threads()

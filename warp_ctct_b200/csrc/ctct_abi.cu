@@ -225,9 +225,9 @@ int launch_gather_t(const void *lp, const int *ys, const int *lx, const int *ly,
     // a joint tensor in pinned host memory is read in place: no fill-size hint on those loads
     if (is_pinned_host(lp)) valid_only |= 2;
     const int64_t want = (total + 256 * 4 - 1) / (256 * 4);
-    // at most one resident wave (8 blocks of 256 threads per SM): every block starts at once, so the
-    // launch behind this one is released as early as possible
-    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    // half a resident wave (4 blocks of 256 threads per SM): every block starts at once, so the launch
+    // behind this one is released at once, and its clearing blocks find room beside these
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 4;
     const int own = static_cast<int>(want < cap ? want : cap);
     clear.first_block = static_cast<unsigned>(own);
     const unsigned grid = static_cast<unsigned>(own) + clear_blocks(clear);
@@ -342,7 +342,7 @@ int launch_logmm(const float *lhs, int64_t lsb, int64_t lsi, int64_t lsk, const 
     a.N = (int)N;
     a.run_flags = run_flags;
     dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 31) / 32), (unsigned)B);
-    k_logmm_exact<<<grid, 256, 0, st>>>(a);
+    launch_pdl(k_logmm_exact, grid, dim3(256), 0, st, a);
     return check_launch("log_matmul");
 }
 
@@ -422,7 +422,7 @@ int launch_logmm_bwd_inst(const LogmmBwdArgs &a, int64_t B, size_t smem, cudaStr
         cudaFuncSetAttribute(k_logmm_bwd_exact<VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("log_matmul_backward smem attribute");
     dim3 grid((unsigned)((a.K + VT - 1) / VT), (unsigned)B);
-    k_logmm_bwd_exact<VT><<<grid, VT, smem, st>>>(a);
+    launch_pdl(k_logmm_bwd_exact<VT>, grid, dim3(VT), smem, st, a);
     return check_launch("log_matmul_backward");
 }
 
@@ -762,10 +762,10 @@ int ctct_b200_log_matmul_tc(const float *f, const float *g, int64_t B, int64_t M
     if (cudaMemsetAsync(flags, 0, 16, st) != cudaSuccess) return check_launch("log_matmul_tc flags");
     cudaEvent_t *slot = prof_slot(3);
     prof_mark(slot, 0, st);
-    k_exp_split<<<static_cast<unsigned>(B * M), 256, 0, st>>>(f, (int)K, ah, al, mf);
+    launch_pdl(k_exp_split, dim3(static_cast<unsigned>(B * M)), dim3(256), 0, st, f, (int)K, ah, al, mf);
     int rc = check_launch("exp_split f");
     if (rc) return rc;
-    k_exp_split<<<static_cast<unsigned>(B * N), 256, 0, st>>>(g, (int)K, bh, bl, mg);
+    launch_pdl(k_exp_split, dim3(static_cast<unsigned>(B * N)), dim3(256), 0, st, g, (int)K, bh, bl, mg);
     rc = check_launch("exp_split g");
     if (rc) return rc;
     prof_mark(slot, 1, st);
@@ -782,7 +782,7 @@ int ctct_b200_log_matmul_tc(const float *f, const float *g, int64_t B, int64_t M
     a.K = (int)K;
     a.flags = flags;
     dim3 grid((unsigned)((M + TC_BM - 1) / TC_BM), (unsigned)((N + TC_BN - 1) / TC_BN), (unsigned)B);
-    k_logmm_tc<<<grid, 128, TC_SMEM_BYTES, st>>>(m_ah, m_al, m_bh, m_bl, a);
+    launch_pdl(k_logmm_tc, grid, dim3(128), TC_SMEM_BYTES, st, m_ah, m_al, m_bh, m_bl, a);
     rc = check_launch("log_matmul_tc");
     if (rc) return rc;
     prof_mark(slot, 2, st);
@@ -840,7 +840,7 @@ int ctct_b200_simple_forward(const float *f, const float *g, const float *den, c
     if (c.total > 0) {
         const int64_t want = (c.total + 255) / 256;
         const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
-        k_simple_compose<<<static_cast<int>(want < cap ? want : cap), 256, 0, st>>>(c);
+        launch_pdl(k_simple_compose, dim3(static_cast<unsigned>(want < cap ? want : cap)), dim3(256), 0, st, c);
         int rc = check_launch("simple_compose");
         if (rc) return rc;
     }
@@ -884,7 +884,7 @@ static int den_backward_tc(const float4 *g4, const float *gout, const float *gra
     w.U1 = (int)U1;
     w.U1p = (int)l.Np;
     w.flags = flags;
-    k_den_weights<<<static_cast<unsigned>(N * T), 128, 0, st>>>(w);
+    launch_pdl(k_den_weights, dim3(static_cast<unsigned>(N * T)), dim3(128), 0, st, w);
     int rc = check_launch("den_weights");
     if (rc) return rc;
     static std::once_flag attr_once;
@@ -926,14 +926,14 @@ static int den_backward_tc(const float4 *g4, const float *gout, const float *gra
         a.flags = flags;
         const unsigned grid = (unsigned)(total < sm_count() ? total : sm_count());
         if (a_mn)
-            k_logmm_bwd_tc<true, false, BW_G_STAGES, BW_G_EBUFS>
-                <<<grid, BW_THREADS, bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS, false), st>>>(pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
+            launch_pdl(k_logmm_bwd_tc<true, false, BW_G_STAGES, BW_G_EBUFS>, dim3(grid), dim3(BW_THREADS),
+                       bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS, false), st, pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
         else if (K <= BW_BK * BW_ARES_KB)  // the whole contraction of A fits the resident buffer
-            k_logmm_bwd_tc<false, true, BW_R_STAGES, BW_R_EBUFS>
-                <<<grid, BW_THREADS, bw_smem_bytes(BW_R_STAGES, BW_R_EBUFS, true), st>>>(pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
+            launch_pdl(k_logmm_bwd_tc<false, true, BW_R_STAGES, BW_R_EBUFS>, dim3(grid), dim3(BW_THREADS),
+                       bw_smem_bytes(BW_R_STAGES, BW_R_EBUFS, true), st, pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
         else
-            k_logmm_bwd_tc<false, false, BW_F_STAGES, BW_F_EBUFS>
-                <<<grid, BW_THREADS, bw_smem_bytes(BW_F_STAGES, BW_F_EBUFS, false), st>>>(pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
+            launch_pdl(k_logmm_bwd_tc<false, false, BW_F_STAGES, BW_F_EBUFS>, dim3(grid), dim3(BW_THREADS),
+                       bw_smem_bytes(BW_F_STAGES, BW_F_EBUFS, false), st, pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
         return check_launch(what);
     };
     // grad_f[t,v] = Ef[t,v] * sum_u P[t,u] Eg[u,v]
@@ -1008,13 +1008,13 @@ static int simple_backward_impl(const float *grads3, const float *grad_out, cons
     p.V = (int)V;
     if (grad_f && T > 0) {
         dim3 grid((unsigned)((T * U1 + 255) / 256), (unsigned)N);
-        k_simple_patch_f<<<grid, 256, 0, st>>>(p);
+        launch_pdl(k_simple_patch_f, grid, dim3(256), 0, st, p);
         int rc = check_launch("simple_patch_f");
         if (rc) return rc;
     }
     if (grad_g) {
         const int64_t warps = N * U1;
-        k_simple_patch_g<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(p, (int)N);
+        launch_pdl(k_simple_patch_g, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, st, p, (int)N);
         int rc = check_launch("simple_patch_g");
         if (rc) return rc;
     }

@@ -54,33 +54,42 @@ struct DenWeightArgs {
     const int *flags;
 };
 
-// one block per (b,t) row
+// one block per (b,t) row.  Every load is issued before any of them is needed (all addresses are in
+// bounds for u < U1), so a block pays one round of memory latency, not two.
 __global__ void __launch_bounds__(128) k_den_weights(const DenWeightArgs a) {
-    if (a.flags[0] | a.flags[1]) return;
+    pdl_wait();
     const int64_t bt = blockIdx.x;
     const int b = static_cast<int>(bt / a.T), t = static_cast<int>(bt - static_cast<int64_t>(b) * a.T);
-    const bool row_ok = a.gout ? true : t < a.lx[b];
-    const int un = a.gout ? a.U1 : min(a.ly[b] + 1, a.U1);
-    const float sc = a.gout ? 0.0f : -a.scale[b];
+    const int u = threadIdx.x;  // U1p <= 128 columns per pass
+    const int f0 = a.flags[0], f1 = a.flags[1];
+    const int lxb = a.gout ? a.T : a.lx[b];
+    const int lyb = a.gout ? a.U1 : a.ly[b];
+    const float scl = a.gout ? 0.0f : a.scale[b];
     const float mfr = a.mf[bt];
-    for (int u = threadIdx.x; u < a.U1p; u += blockDim.x) {
-        float p = 0.0f;
-        if (row_ok && u < un) {
-            float w;
+    for (int u0 = 0; u0 < a.U1p; u0 += blockDim.x) {
+        const int uu = u0 + u;
+        float w = 0.0f, mgv = 0.0f, dv = 0.0f;
+        if (uu < a.U1) {
             if (a.gout) {
-                w = a.gout[bt * a.U1 + u];
+                w = a.gout[bt * a.U1 + uu];
             } else {
-                const float4 g3 = a.grads3[bt * a.U1 + u];
-                w = sc * (g3.x + g3.y + g3.z);
+                const float4 g3 = a.grads3[bt * a.U1 + uu];
+                w = -(g3.x + g3.y + g3.z);
             }
-            if (w != 0.0f) p = w * ex2((mfr + a.mg[static_cast<int64_t>(b) * a.U1 + u] - a.den[bt * a.U1 + u]) * LOG2E);
+            mgv = a.mg[static_cast<int64_t>(b) * a.U1 + uu];
+            dv = a.den[bt * a.U1 + uu];
         }
+        if (f0 | f1) return;  // the exact kernel does the work
+        if (uu >= a.U1p) continue;
+        float p = 0.0f;
+        if (!a.gout) w *= scl;
+        const bool live = t < lxb && uu < (a.gout ? a.U1 : min(lyb + 1, a.U1));
+        if (live && w != 0.0f) p = w * ex2((mfr + mgv - dv) * LOG2E);
         const __nv_bfloat16 h = __float2bfloat16_rn(p);
-        a.ph[bt * a.U1p + u] = h;
-        a.pl[bt * a.U1p + u] = __float2bfloat16_rn(p - __bfloat162float(h));
+        a.ph[bt * a.U1p + uu] = h;
+        a.pl[bt * a.U1p + uu] = __float2bfloat16_rn(p - __bfloat162float(h));
     }
 }
-
 
 struct LogmmBwdTcArgs {
     const float *mx;   // (B, M) row maxima of src
@@ -114,6 +123,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) k_logmm_bwd_tc(const __grid_con
                                                                 const LogmmBwdTcArgs a) {
     extern __shared__ unsigned char bw_raw[];
     __shared__ int skip;
+    pdl_wait();
     if (threadIdx.x == 0) skip = a.flags[0] | a.flags[1];
     __syncthreads();
     if (skip) return;  // the exact kernel does the work (same decision for the whole CTA)

@@ -44,6 +44,8 @@ constexpr unsigned TC_SPIN_LIMIT = 1u << 23;                      // polls per w
 __global__ void __launch_bounds__(256) k_exp_split(const float *__restrict__ x, int K, __nv_bfloat16 *__restrict__ hi,
                                                    __nv_bfloat16 *__restrict__ lo, float *__restrict__ mx) {
     __shared__ float red[8];
+    pdl_wait();
+    pdl_trigger();  // the next launch (the other operand, or the GEMM's one CTA per SM) may move in
     const int64_t r = blockIdx.x;
     const float *row = x + r * K;
     const float NINF = -__int_as_float(0x7f800000);
@@ -217,6 +219,7 @@ __global__ void __launch_bounds__(128) k_logmm_tc(const __grid_constant__ CUtens
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = *slot_ptr;
     bool ok = true;
+    pdl_wait();  // barriers and TMEM were set up while the kernel before this one drained
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer

@@ -34,6 +34,7 @@ struct LogmmArgs {
 __global__ void __launch_bounds__(256) k_logmm_exact(const LogmmArgs a) {
     __shared__ float As[32][33];  // [i][k]
     __shared__ float Bs[32][33];  // [k][j]
+    pdl_wait();
     if (a.run_flags != nullptr && a.run_flags[0] == 0 && a.run_flags[1] == 0) return;
     const int b = blockIdx.z;
     const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
@@ -106,6 +107,7 @@ struct ComposeArgs {
 };
 
 __global__ void __launch_bounds__(256) k_simple_compose(const ComposeArgs a) {
+    pdl_wait();
     const int U = a.U1 - 1;
     for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < a.total;
          e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -151,6 +153,7 @@ struct LogmmBwdArgs {
 template <int VT>
 __global__ void __launch_bounds__(VT) k_logmm_bwd_exact(const LogmmBwdArgs a) {
     extern __shared__ float sm[];
+    pdl_wait();
     if (a.run_flags != nullptr && a.run_flags[0] == 0 && a.run_flags[1] == 0) return;
     const int b = blockIdx.y;
     const int k = blockIdx.x * VT + threadIdx.x;
@@ -213,6 +216,7 @@ struct PatchArgs {
 // grad_f[n,t,0] += sum_u g0;  grad_f[n,t,ys[j]] += g2[t,j] + g1[t,j+1].  One thread per (t, j);
 // labels may repeat inside an utterance, hence atomics.
 __global__ void __launch_bounds__(256) k_simple_patch_f(const PatchArgs a) {
+    pdl_wait();
     const int n = blockIdx.y;
     const int U = a.U1 - 1;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -233,6 +237,7 @@ __global__ void __launch_bounds__(256) k_simple_patch_f(const PatchArgs a) {
 
 // grad_g[n,u,{0, ys[u-1], ys[u]}] += sum_t of the three slots.  One warp per (n,u).
 __global__ void __launch_bounds__(256) k_simple_patch_g(const PatchArgs a, int N) {
+    pdl_wait();
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (w >= N * a.U1) return;
     const int n = w / a.U1, u = w - n * a.U1;
