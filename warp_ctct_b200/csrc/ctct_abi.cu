@@ -12,6 +12,7 @@
 #include "simple.cuh"
 #include "logmm_tc.cuh"
 #include "logmm_bwd_tc.cuh"
+#include "logmm_bwd_fused.cuh"
 
 using namespace ctct;
 
@@ -903,6 +904,36 @@ static int den_backward_tc(const float4 *g4, const float *gout, const float *gra
         !make_plane_map(&m_g_h, bh, N, U1, V, BW_BK) || !make_plane_map(&m_g_l, bl, N, U1, V, BW_BK)) {
         snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "cuTensorMapEncodeTiled failed");
         return CTCT_ERR_LAUNCH;
+    }
+    if (grad_f && grad_g && U1 <= 128 && getenv("CTCT_B200_NO_FUSED_BWD") == nullptr) {
+        // both gradients in one pass over the Ef planes
+        static std::once_flag fused_once;
+        std::call_once(fused_once, [] {
+            cudaFuncSetAttribute(k_den_bwd_fused, cudaFuncAttributeMaxDynamicSharedMemorySize, FU_SMEM_BYTES);
+        });
+        CUtensorMap m_out;
+        if (!make_f32_tile_map(&m_out, grad_f, N, T, V)) {
+            snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "cuTensorMapEncodeTiled failed");
+            return CTCT_ERR_LAUNCH;
+        }
+        DenBwdFusedArgs fa;
+        fa.g = g;
+        fa.mg = mg;
+        fa.grad_g = grad_g;
+        fa.T = (int)T;
+        fa.U1 = (int)U1;
+        fa.V = (int)V;
+        fa.slabs = (int)((V + FU_V - 1) / FU_V);
+        const int64_t items = (int64_t)fa.slabs * N;
+        if (items > 0x7fffffff) return CTCT_ERR_UNSUPPORTED;
+        fa.items = (int)items;
+        fa.flags = flags;
+        const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
+        launch_pdl(k_den_bwd_fused, dim3(grid), dim3(FU_THREADS), FU_SMEM_BYTES, st, m_pk_h, m_pk_l, m_f_h, m_f_l, m_g_h,
+                   m_g_l, m_out, fa);
+        rc = check_launch("den_bwd_fused");
+        prof_mark(slot, 1, st);
+        return rc;
     }
     const int tiles_n = (int)((V + BW_BN - 1) / BW_BN);
     auto launch = [&](bool a_mn, const CUtensorMap &pa_h, const CUtensorMap &pa_l, const CUtensorMap &pb_h,
