@@ -62,13 +62,14 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
     const unsigned eg = ring + FU_STAGES * FU_STAGE_BYTES;
     const unsigned bars = eg + FU_EG_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };              // stage loaded
-    auto empty_bar = [&](int s) { return bars + 8u * (2 + s); };       // stage free again (its store has read it)
+    auto empty_bar = [&](int s) { return bars + 8u * (2 + s); };       // Ef part free again (its store has read it)
+    auto p_empty = [&](int s) { return bars + 8u * (14 + s); };        // P part free again (both GEMMs complete)
     auto done_bar = [&](int s) { return bars + 8u * (4 + s); };        // both GEMMs of the stage complete
     auto ready_bar = [&](int s) { return bars + 8u * (6 + s); };       // grad_f tile written, store may go
     auto d1_empty = [&](int q) { return bars + 8u * (8 + q); };        // accumulator of GEMM 1 read out
     const unsigned eg_full = bars + 8u * 10, eg_empty = bars + 8u * 11;
     const unsigned d2_full = bars + 8u * 12, d2_empty = bars + 8u * 13;
-    constexpr int NBARS = 14;
+    constexpr int NBARS = 16;
     const unsigned slot_addr = bars + 8u * NBARS;
     unsigned *slot_ptr = reinterpret_cast<unsigned *>(fu_raw + (slot_addr - raw));
     unsigned char *ring_ptr = fu_raw + (ring - raw);
@@ -78,7 +79,8 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
     constexpr unsigned TMEM_COLS = 256;  // D1[0] at 0, D1[1] at 64, D2 at 128
 
     if (threadIdx.x == 0) {
-        for (int q = 0; q < NBARS; ++q) mbar_init(bars + 8u * q, q == 13 ? BW_EPI_WARPS : 1);
+        // full: two arrivals (P loads, Ef loads); d2_empty: one per epilogue warp
+        for (int q = 0; q < NBARS; ++q) mbar_init(bars + 8u * q, q == 13 ? BW_EPI_WARPS : (q < 2 ? 2 : 1));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -116,23 +118,31 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
             for (int tb = 0; tb < ntb; ++tb, ++tbc) {
                 const int s = tbc & 1;
                 const unsigned ph = (tbc >> 1) & 1;
-                ok = mbar_wait(empty_bar(s), ph ^ 1);
-                if (!ok) break;
+                // the P part comes back as soon as the MMAs that read it are done, the Ef part (which
+                // the grad_f tile is written over) only when its store has read it
                 const unsigned st = ring + s * FU_STAGE_BYTES;
                 const unsigned bar = full_bar(s);
                 const int t0 = tb * FU_T;
-                mbar_expect_tx(bar, FU_STAGE_BYTES);
+                ok = mbar_wait(p_empty(s), ph ^ 1);
+                if (!ok) break;
+                mbar_expect_tx(bar, FU_P_BYTES);
                 tma_load_3d(st, &map_ph, bar, 0, t0, b);
                 tma_load_3d(st + BW_A_PLANE, &map_ph, bar, 64, t0, b);
                 tma_load_3d(st + 2 * BW_A_PLANE, &map_pl, bar, 0, t0, b);
                 tma_load_3d(st + 3 * BW_A_PLANE, &map_pl, bar, 64, t0, b);
+                armed |= 1u << s;
+                armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+                ok = mbar_wait(empty_bar(s), ph ^ 1);
+                if (!ok) {
+                    mbar_expect_tx(bar, 0);  // second arrival of the phase, so that the P loads can be waited for
+                    break;
+                }
+                mbar_expect_tx(bar, FU_E_BYTES);
                 const unsigned ef = st + FU_P_BYTES;
                 tma_load_3d(ef, &map_fh, bar, v0, t0, b);
                 tma_load_3d(ef + BW_A_PLANE / 2, &map_fh, bar, v0, t0 + 64, b);
                 tma_load_3d(ef + BW_A_PLANE, &map_fl, bar, v0, t0, b);
                 tma_load_3d(ef + BW_A_PLANE + BW_A_PLANE / 2, &map_fl, bar, v0, t0 + 64, b);
-                armed |= 1u << s;
-                armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
             }
         }
         if (!ok) atomicExch(a.flags, 1);
@@ -195,6 +205,7 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
                     umma_bf16(d2, al, bh, idesc2, 1u);
                 }
                 umma_commit(done_bar(s));
+                umma_commit(p_empty(s));
                 if (tb == ntb - 1) umma_commit(d2_full);
             }
         }
