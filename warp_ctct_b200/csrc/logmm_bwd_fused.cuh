@@ -175,6 +175,7 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
                 for (int kb = 0; kb < 2; ++kb) {
 #pragma unroll
                     for (int k4 = 0; k4 < 4; ++k4) {
+                        if (kb * 64 + k4 * 16 >= a.U1) continue;  // columns of P beyond U+1 are zero
                         const uint64_t ah = umma_pack(pa + (kb * BW_A_PLANE + k4 * 32) / 16);
                         const uint64_t al = umma_pack(pa + (2 * BW_A_PLANE + kb * BW_A_PLANE + k4 * 32) / 16);
                         const uint64_t bh = umma_pack(gb + (kb * 8192 + k4 * 2048) / 16);
@@ -234,6 +235,21 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
         for (int item = blockIdx.x, i = 0; item < a.items; item += gridDim.x, ++i) {
             int v0, b;
             item_coords(item, v0, b);
+            // this thread's 32 values of g and its row maximum for the item's grad_g: requested now,
+            // needed only after the last frame block
+            const int64_t grow = static_cast<int64_t>(b) * a.U1 + r;
+            const int gcol = v0 + c * 32;
+            float4 gx[8];
+            float mgr = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) gx[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < a.U1) {
+                mgr = __ldg(a.mg + grow);
+                const float4 *src = reinterpret_cast<const float4 *>(a.g + grow * a.V + gcol);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (gcol + 4 * j < a.V) gx[j] = __ldg(src + j);
+            }
             for (int tb = 0; tb < ntb; ++tb, ++tbc) {
                 const int s = tbc & 1, q = tbc & 1;
                 ok = all_agree(mbar_wait(done_bar(s), (tbc >> 1) & 1));
@@ -287,26 +303,19 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
             __syncwarp();
             if (lane == 0) mbar_arrive(d2_empty);
             if (r < a.U1) {
-                const int64_t row = static_cast<int64_t>(b) * a.U1 + r;
-                const float mgr = __ldg(a.mg + row);
-                const int col = v0 + c * 32;
-                const float4 *src = reinterpret_cast<const float4 *>(a.g + row * a.V + col);
-                float4 *dst = reinterpret_cast<float4 *>(a.grad_g + row * a.V + col);
-                float4 x[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) x[j] = (col + 4 * j < a.V) ? __ldg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 *dst = reinterpret_cast<float4 *>(a.grad_g + grow * a.V + gcol);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    if (col + 4 * j < a.V) {
+                    if (gcol + 4 * j < a.V) {
                         const float d0 = __uint_as_float(d[4 * j]), d1v = __uint_as_float(d[4 * j + 1]);
                         const float d2v = __uint_as_float(d[4 * j + 2]), d3 = __uint_as_float(d[4 * j + 3]);
                         float4 o;
                         // a zero sum stays zero even where exp() would overflow or g is -inf
-                        o.x = d0 != 0.0f ? d0 * ex2((x[j].x - mgr) * LOG2E) : 0.0f;
-                        o.y = d1v != 0.0f ? d1v * ex2((x[j].y - mgr) * LOG2E) : 0.0f;
-                        o.z = d2v != 0.0f ? d2v * ex2((x[j].z - mgr) * LOG2E) : 0.0f;
-                        o.w = d3 != 0.0f ? d3 * ex2((x[j].w - mgr) * LOG2E) : 0.0f;
-                        dst[j] = o;
+                        o.x = d0 != 0.0f ? d0 * ex2((gx[j].x - mgr) * LOG2E) : 0.0f;
+                        o.y = d1v != 0.0f ? d1v * ex2((gx[j].y - mgr) * LOG2E) : 0.0f;
+                        o.z = d2v != 0.0f ? d2v * ex2((gx[j].z - mgr) * LOG2E) : 0.0f;
+                        o.w = d3 != 0.0f ? d3 * ex2((gx[j].w - mgr) * LOG2E) : 0.0f;
+                        __stcs(dst + j, o);
                     }
                 }
             }
