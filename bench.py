@@ -44,10 +44,11 @@ UNIT = "utt/s"
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from the
 # ncu captures summarised in profiles/: c2 = the lattice launch with its clearing blocks
-# (ctct_loss_c2_kernels.md); c4 = the grad_f GEMM, captured at half the batch (c4s,
-# simple_loss_c4s_kernels.md) and doubled, since traffic is proportional to the number of utterances.
-NCU_TRAFFIC_PER_LAUNCH = {"c2": 10796544 + 1038705000, "c4s": 209618176 + 91585792,
-                          "c4": 2 * (209618176 + 91585792)}
+# (ctct_loss_c2_kernels.md); c4 = the fused backward kernel of the denominator, captured at half the
+# batch (c4s, simple_loss_c4s_kernels.md) and doubled, since traffic is proportional to the number
+# of utterances.
+NCU_TRAFFIC_PER_LAUNCH = {"c2": 10796544 + 1038705000, "c4s": 187469824 + 113467392,
+                          "c4": 2 * (187469824 + 113467392)}
 
 
 def workload_string(name, n_gpus):
@@ -591,12 +592,19 @@ def run_b200_simple(args):
     hbm_peak, hbm_kind = peaks()
     flops = 2.0 * B * T * U1 * V                       # one multiply-add per (t, u, v): the contraction itself
     tc_ach = flops / (k_ms["logmm_tc"] * 1e-3) / 1e12
-    gf_bytes = 4 * (2 * B * T * V) + 4 * B * U1 * V    # f read, grad_f written, Eg planes (hi + lo) read
-    gg_bytes = 4 * (2 * B * U1 * V) + 4 * B * T * V    # g read, grad_g written, Ef planes (hi + lo) read
+    fused = U1 <= 128  # both gradients in one pass over the Ef planes (k_den_bwd_fused)
+    if fused:
+        # Ef planes (hi + lo) read, grad_f written, g read, grad_g written, Eg planes read
+        gf_bytes = 4 * (2 * B * T * V) + 4 * (3 * B * U1 * V)
+        gg_bytes = 0
+        name = "k_den_bwd_fused (grad_f = Ef * (P Eg) and grad_g = Eg * (P^T Ef) in one pass: tcgen05 GEMMs) + k_den_weights"
+    else:
+        gf_bytes = 4 * (2 * B * T * V) + 4 * B * U1 * V    # f read, grad_f written, Eg planes (hi + lo) read
+        gg_bytes = 4 * (2 * B * U1 * V) + 4 * B * T * V    # g read, grad_g written, Ef planes (hi + lo) read
+        name = "k_logmm_bwd_tc (grad_f = Ef * (P Eg): tcgen05 GEMM with exp epilogue) + k_den_weights"
     gf_ach = gf_bytes / (k_ms["den_backward_grad_f"] * 1e-3) / 1e9
-    # dominant launch of the step: the tensor-core GEMM that writes grad_f (its interval also holds the
-    # small weight kernel); it is bound by streaming f in and grad_f out, not by the tensor pipe
-    roofline = {"kernel": "k_logmm_bwd_tc (grad_f = Ef * (P Eg): tcgen05 GEMM with exp epilogue) + k_den_weights",
+    # dominant launch of the step; it is bound by streaming the planes in and grad_f out, not by the tensor pipe
+    roofline = {"kernel": name,
                 "bound": "hbm", "achieved": gf_ach, "peak": hbm_peak, "unit": "GB/s", "frac": gf_ach / hbm_peak,
                 "peak_source": f"of {hbm_kind}", "algorithmic_bytes": gf_bytes,
                 "traffic": NCU_TRAFFIC_PER_LAUNCH.get(args.workload)}
@@ -613,6 +621,9 @@ def run_b200_simple(args):
     kernels["logmm_tc"].update({"TFLOP/s": tc_ach, "operand_GB/s": plane_bytes / (k_ms["logmm_tc"] * 1e-3) / 1e9,
                                 "tensor_roofline": tensor})
     for key, nbytes in (("den_backward_grad_f", gf_bytes), ("den_backward_grad_g", gg_bytes)):
+        if nbytes == 0:
+            kernels[key]["note"] = "exact fall-back kernel only (a flag check); the fused kernel is in den_backward_grad_f"
+            continue
         kernels[key].update({"GB/s": nbytes / (k_ms[key] * 1e-3) / 1e9, "frac": nbytes / (k_ms[key] * 1e-3) / 1e9 / hbm_peak,
                              "hbm_peak_source": f"of {hbm_kind}"})
     kernels["sum_ms"] = sum(k_ms.values())
@@ -685,7 +696,7 @@ def run_b200_simple(args):
                    "l2": f"inputs larger than L2: f {4 * B * T * V / 1e6:.0f} MB, g {4 * B * U1 * V / 1e6:.0f} MB, "
                          f"their gradients as much again, bf16 planes {plane_bytes / 1e6:.0f} MB (L2 is 126 MB)",
                    "shard_weights": shard_weights(lx_g, ly_g, plan)},
-        "clocks": clocks, "e2e": e2e, "gpu_launches": 13 * args.steps * world,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": (12 if U1 <= 128 else 13) * args.steps * world,
         "roofline": roofline, "kernels": kernels, "host_enqueue_us_per_step": host_us,
         "profiled_pass_ms_per_step": ms_profiled / args.steps,
     }
