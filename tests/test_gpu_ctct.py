@@ -449,3 +449,24 @@ def test_forward_and_backward_replay_from_a_cuda_graph(W):
         loss.backward()
         assert torch.equal(static_loss.detach(), loss.detach())
         assert torch.equal(static_lp.grad, eager.grad)
+
+
+def test_sharded_loss_on_one_rank_and_global_batch(W):
+    """sharded_ctct_loss without a process group equals ctct_loss; global_batch rescales 'mean' and its
+    gradient (loss and gradient of a shard of a 4x larger batch are a quarter each)."""
+    from warp_ctct_b200.sharded import sharded_ctct_loss
+    lp, ys, lx, ly = make_case(4, 64, 17, 512, sigma=1.5, seed=51, lx_range=(30, 64), ly_range=(3, 16), cap_half=True)
+    ys_t, lx_t, ly_t = _dev(ys, lx, ly)
+    a = torch.from_numpy(lp).to(DEV).requires_grad_(True)
+    b = torch.from_numpy(lp).to(DEV).requires_grad_(True)
+    c = torch.from_numpy(lp).to(DEV).requires_grad_(True)
+    l1 = sharded_ctct_loss(a, ys_t, lx_t, ly_t, reduction="mean")
+    l2 = W.ctct_loss(b, ys_t, lx_t, ly_t, reduction="mean")
+    l3 = sharded_ctct_loss(c, ys_t, lx_t, ly_t, global_batch=16, reduction="mean")
+    for l in (l1, l2, l3):
+        l.backward()
+    assert torch.equal(l1.detach(), l2.detach()) and torch.equal(a.grad, b.grad)
+    assert abs(l3.item() * 4 - l2.item()) <= 1e-6 * abs(l2.item())
+    assert (c.grad * 4 - b.grad).abs().max().item() <= 1e-6
+    loss_h, grad_h = W.ctct_loss_and_grad(b.detach(), ys_t, lx_t, ly_t, reduction="mean", global_batch=16)
+    assert torch.equal(loss_h, l3.detach()) and torch.equal(grad_h, c.grad)

@@ -286,3 +286,23 @@ def test_reference_style_simple_class(W):
     fused.sum().backward()
     np.testing.assert_allclose(costs.detach().cpu().numpy(), fused.detach().cpu().numpy(), rtol=1e-5)
     assert (a.grad - c.grad).abs().max().item() < 5e-5 and (b.grad - d.grad).abs().max().item() < 5e-5
+
+
+def test_sharded_simple_loss_on_one_rank_equals_the_plain_call(W):
+    """Without a process group the sharded entry point is the plain loss (global batch = local batch)."""
+    from warp_ctct_b200.sharded import sharded_ctct_simple_loss
+    N, T, U1, V = 3, 50, 12, 128
+    f, g, ys, lx, ly = _case(N, T, U1, V, 33, (25, 50), (3, 11))
+    f_t, g_t, ys_t, lx_t, ly_t = _dev(f, g, ys, lx, ly)
+    a, b = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    c, d = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    l1 = sharded_ctct_simple_loss(a, b, ys_t, lx_t, ly_t, reduction="mean")
+    l2 = W.ctct_simple_loss(c, d, ys_t, lx_t, ly_t, reduction="mean")
+    l1.backward()
+    l2.backward()
+    assert abs(l1.item() - l2.item()) <= 1e-6 * abs(l2.item())
+    # the label patches are atomic adds (labels may repeat), so two runs agree to rounding, not bitwise
+    assert (a.grad - c.grad).abs().max().item() <= 1e-6 and (b.grad - d.grad).abs().max().item() <= 1e-6
+    # a shard of a larger batch: 'mean' divides by the global batch
+    l3 = sharded_ctct_simple_loss(f_t, g_t, ys_t, lx_t, ly_t, global_batch=4 * N, reduction="mean")
+    assert abs(l3.item() * 4 - l2.item()) <= 1e-6 * abs(l2.item())
