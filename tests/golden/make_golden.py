@@ -18,7 +18,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2 and "WARP_CTCT_REFERENCE" not in os.environ:
+    raise SystemExit("usage: python make_golden.py <checkout of maxwellzh/warp-ctct>  (or set WARP_CTCT_REFERENCE)")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ["WARP_CTCT_REFERENCE"]
 sys.path.insert(0, REF)
 import ref_ctct as R  # noqa: E402
 

@@ -60,7 +60,7 @@ def test_log_matmul_matches_oracle(W, B, M, N, K):
 @pytest.mark.parametrize("B,M,N,K,scale", [(2, 130, 70, 256, 1.0), (3, 33, 17, 64, 2.0), (1, 257, 101, 4096, 1.0),
                                            (2, 128, 128, 520, 3.0), (1, 300, 260, 136, 1.0)])
 def test_log_matmul_tensor_core_matches_oracle(W, B, M, N, K, scale):
-    """tcgen05 path: bf16 hi+lo operands, fp32 accumulation; the float64 oracle is the judge."""
+    """tcgen05 path: bf16 hi+lo operands, fp32 accumulation; the result is held to the float64 oracle."""
     from warp_ctct_b200.simple import log_matmul, log_matmul_tc
     rng = np.random.default_rng(B * 7 + K)
     f = (scale * rng.standard_normal((B, M, K))).astype(np.float32)
@@ -146,7 +146,7 @@ def test_logmmexp_autograd_matches_logsumexp(W):
 @pytest.mark.parametrize("B,M,N,K", [(2, 150, 70, 128), (1, 40, 140, 264)])
 def test_logmmexp_autograd_on_tensor_cores(W, B, M, N, K):
     """The reference's composition LogMMExp(f, g^T) takes the tensor-core kernels in both directions;
-    signed upstream gradients, float64 logsumexp as the judge."""
+    signed upstream gradients, checked against float64 logsumexp."""
     from warp_ctct_b200.simple import _tc_operands
     rng = np.random.default_rng(K)
     f = torch.from_numpy(rng.standard_normal((B, M, K)).astype(np.float32)).to(DEV)
