@@ -321,6 +321,26 @@ def run_b200(args):
         kernels["lattice_and_clear"] = {"ms": k_ms["lattice"], "GB/s": ach, "frac": ach / peak,
                                         "note": "one launch: 2 lattice CTAs per utterance + blocks that zero the gradient"}
         kernels["dense_patch"] = {"ms": k_ms["dense_patch"]}
+        # the lattice recursion by itself: a few steps with the clearing moved out of its launch
+        # (one-pass dense gradient in the backward pass), event recording on
+        W.PREZERO = False
+        try:
+            n_alone = 10
+            _lib.check(lib.ctct_b200_profile_enable(3 * n_alone), "profile_enable")
+            for _ in range(n_alone):
+                step()
+            torch.cuda.synchronize(dev)
+            buf2 = np.zeros((3 * n_alone, 4), np.float32)
+            kinds2 = np.zeros((3 * n_alone,), np.int32)
+            n2 = lib.ctct_b200_profile_read(buf2.ctypes.data, kinds2.ctypes.data, 3 * n_alone)
+            lib.ctct_b200_profile_disable()
+            alone = buf2[:n2][kinds2[:n2] == 0][:, 1]
+            rows = max(int(lx.max()), 1)
+            kernels["lattice_alone"] = {"ms": float(alone.mean()), "ns_per_row": 1e6 * float(alone.mean()) / rows,
+                                        "note": "alpha and beta CTAs of all utterances run concurrently; rows = frames of "
+                                                "the longest utterance; measured with the clearing blocks taken out"}
+        finally:
+            W.PREZERO = True
     else:
         kernels["lattice"] = {"ms": k_ms["lattice"], "ns_per_row": 1e6 * k_ms["lattice"] / max(int(lx.max()), 1),
                               "note": "alpha and beta CTAs of all utterances run concurrently; rows = longest utterance"}
