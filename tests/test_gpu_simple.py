@@ -306,3 +306,28 @@ def test_sharded_simple_loss_on_one_rank_equals_the_plain_call(W):
     # a shard of a larger batch: 'mean' divides by the global batch
     l3 = sharded_ctct_simple_loss(f_t, g_t, ys_t, lx_t, ly_t, global_batch=4 * N, reduction="mean")
     assert abs(l3.item() * 4 - l2.item()) <= 1e-6 * abs(l2.item())
+
+
+@pytest.mark.parametrize("shape,lx,ly", [
+    ((2, 1, 2, 64), [1, 1], [1, 1]),            # one frame, one label
+    ((1, 3, 2, 72), [3], [1]),
+    ((2, 129, 2, 64), [129, 70], [1, 1]),       # one frame past a 128-frame block
+    ((1, 5, 200, 128), [5], [4]),               # far more contexts than frames, U+1 > 128 (separate GEMM kernels)
+    ((3, 128, 128, 64), [128, 100, 64], [60, 50, 20]),  # exactly one tile each way
+])
+def test_simple_loss_tensor_core_edge_shapes(W, shape, lx, ly):
+    N, T, U1, V = shape
+    rng = np.random.default_rng(N * 100 + T)
+    f = rng.standard_normal((N, T, V)).astype(np.float32)
+    g = rng.standard_normal((N, U1, V)).astype(np.float32)
+    ys = rng.integers(1, V, (N, max(U1 - 1, 0))).astype(np.int32)
+    lx, ly = np.array(lx, np.int32), np.array(ly, np.int32)
+    f_t, g_t = [t.requires_grad_(True) for t in _dev(f, g)]
+    ys_t, lx_t, ly_t = _dev(ys, lx, ly)
+    costs = W.ctct_simple_loss(f_t, g_t, ys_t, lx_t, ly_t, reduction="none")
+    costs.sum().backward()
+    c_ref, gf_ref, gg_ref = oracle.simple_loss(f, g, ys, lx, ly, True, dtype=np.float64)
+    assert np.isfinite(c_ref).all()
+    np.testing.assert_allclose(costs.detach().cpu().numpy(), c_ref, rtol=1e-5)
+    np.testing.assert_allclose(f_t.grad.cpu().numpy(), gf_ref, atol=1e-4, rtol=2e-5)
+    np.testing.assert_allclose(g_t.grad.cpu().numpy(), gg_ref, atol=1e-4, rtol=2e-5)
