@@ -1038,7 +1038,7 @@ static int simple_backward_impl(const float *grads3, const float *grad_out, cons
     p.U1 = (int)U1;
     p.V = (int)V;
     if (grad_f && T > 0) {
-        dim3 grid((unsigned)((T * U1 + 255) / 256), (unsigned)N);
+        dim3 grid((unsigned)((T + 7) / 8), (unsigned)N);  // one warp per frame
         launch_pdl(k_simple_patch_f, grid, dim3(256), 0, st, p);
         int rc = check_launch("simple_patch_f");
         if (rc) return rc;

@@ -213,26 +213,34 @@ struct PatchArgs {
     int T, U1, V;
 };
 
-// grad_f[n,t,0] += sum_u g0;  grad_f[n,t,ys[j]] += g2[t,j] + g1[t,j+1].  One thread per (t, j);
-// labels may repeat inside an utterance, hence atomics.
+// grad_f[n,t,0] += sum_u g0;  grad_f[n,t,ys[j]] += g2[t,j] + g1[t,j+1].  One warp per (n,t): the
+// blank column gets the warp's sum in one add instead of one atomic per context on the same
+// address; labels may repeat inside an utterance, hence atomics for the label columns.
 __global__ void __launch_bounds__(256) k_simple_patch_f(const PatchArgs a) {
     pdl_wait();
     const int n = blockIdx.y;
     const int U = a.U1 - 1;
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= a.T * a.U1) return;
-    const int t = idx / a.U1, j = idx - t * a.U1;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
     const int Tn = max(0, min(a.lx[n], a.T)), Un = max(0, min(a.ly[n], U));
-    if (t >= Tn || j > Un) return;
+    if (t >= Tn) return;
     const int64_t nt = static_cast<int64_t>(n) * a.T + t;
     const float4 *g3 = a.grads3 + nt * a.U1;
     const float sc = a.scale[n];
     float *row = a.grad_f + nt * a.V;
-    atomicAdd(row, sc * g3[j].x);  // blank column collects slot 0 of every context
-    if (j < Un) {
-        const int v = min(max(a.ys[static_cast<int64_t>(n) * U + j], 0), a.V - 1);
-        atomicAdd(row + v, sc * (g3[j].z + g3[j + 1].y));
+    const int *y = a.ys + static_cast<int64_t>(n) * U;
+    float blank = 0.0f;
+    for (int j = lane; j <= Un; j += 32) {
+        const float4 cur = g3[j];
+        blank += cur.x;
+        if (j < Un) {
+            const int v = min(max(y[j], 0), a.V - 1);
+            atomicAdd(row + v, sc * (cur.z + g3[j + 1].y));
+        }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) blank += __shfl_xor_sync(0xffffffffu, blank, o);
+    if (lane == 0) atomicAdd(row, sc * blank);  // a label equal to the blank index lands here too
 }
 
 // grad_g[n,u,{0, ys[u-1], ys[u]}] += sum_t of the three slots.  One warp per (n,u).
