@@ -422,12 +422,12 @@ def run_b200(args):
     ms_e = timed(e2e_step, e2e_steps)
     ms_c = timed(e2e_copy_step, e2e_steps)
     small = ys_h.numel() * 4 + lx_h.numel() * 4 + ly_h.numel() * 4
-    # one 64-byte request per picked element (the gather asks for 64-byte L2 fills)
-    h2d = rows_valid * 3 * 64 + small
+    # one 32-byte sector per picked element (host-resident tensors are read without a fill-size hint)
+    h2d = rows_valid * 3 * 32 + small
     e2e = {"value": G * e2e_steps / (ms_e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(h2d * world),
            "d2h_bytes_per_step": 4 * world, "steps": e2e_steps,
            "note": "ctct_loss_and_grad on the joint tensor in pinned host memory: the gather kernel reads the 3 "
-                   "log-probs per valid row in place over PCIe (64-byte requests), labels and lengths are copied, "
+                   "log-probs per valid row in place over PCIe (one 32-byte sector each), labels and lengths are copied, "
                    "the dense gradient stays on the device, the loss scalar is read back",
            "full_copy": {"value": G * e2e_steps / (ms_c * 1e-3), "unit": UNIT,
                          "h2d_bytes_per_step": int((lp_host.numel() * esize + small) * world),
