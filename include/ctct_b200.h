@@ -29,6 +29,12 @@ extern "C" {
 #define CTCT_ERR_UNSUPPORTED (-4)/* size outside what the kernels were built for        */
 #define CTCT_ERR_STATIC_SCRATCH (-5) /* problem needs more scratch than the built-in buffer holds */
 
+/* Largest U+1 (label contexts per utterance) any entry point takes: one staged pair of lattice
+ * rows (32 bytes per context) must fit the shared memory of a thread block.
+ * ctct_b200_workspace_bytes returns 0 beyond it and the forward entry points refuse with
+ * CTCT_ERR_UNSUPPORTED before anything is launched. */
+#define CTCT_MAX_U1 7019
+
 /* element type of the joint tensor and of the dense gradient */
 #define CTCT_F32 0
 #define CTCT_F16 1
@@ -58,6 +64,11 @@ size_t ctct_b200_workspace_bytes(int64_t N, int64_t T, int64_t U1, int want_grad
  *         log-probs per (n,t,u), one 16-byte record {g0,g1,g2,0} each
  * Labels are only dereferenced for u < ly[n]; frames t >= lx[n] and contexts
  * u > ly[n] of log_probs are never read.
+ * A label outside [0, V) is CLAMPED into that range, silently, by every kernel that indexes the
+ * vocabulary with it (gather, patches of the dense gradients, the simple-loss composition): the
+ * result is then a finite loss for a different label sequence.  The reference's torch.gather
+ * raises a device-side assert for such a label instead; validate labels on the host if they
+ * may be corrupt.
   *   log_probs may also point to pinned (page-locked, device-accessible) HOST memory: the gather
  *   kernel is the only reader and fetches just the three elements it needs per row over PCIe.
  *   Every other pointer must be device memory.
@@ -220,6 +231,11 @@ int ctct_b200_log_matmul(const float *lhs, int64_t lhs_stride_b, int64_t lhs_str
  * Replaces log_matmul of csrc/binding.cpp:224-245 on the loss path (warp_ctct/__init__.py:195-200).
  */
 size_t ctct_b200_log_matmul_tc_workspace_bytes(int64_t B, int64_t M, int64_t N, int64_t K);
+/* Test hook (no counterpart in the reference): byte offset, inside that workspace, of four int32
+ * status words the tensor-core kernels raise: [0] a bounded wait ran out, [1] a max-shifted sum
+ * underflowed.  Either one non-zero means the exact kernels produced the results of the calls
+ * that used the workspace; all zero means the tensor-core results stand. */
+size_t ctct_b200_log_matmul_tc_flags_offset(int64_t B, int64_t M, int64_t N, int64_t K);
 int ctct_b200_log_matmul_tc(const float *f, const float *g, int64_t B, int64_t M, int64_t N, int64_t K, float *den,
                             void *workspace, size_t workspace_bytes, void *stream);
 

@@ -52,6 +52,13 @@ def test_workspace_and_buffer_sizes(built):
     assert 32 * 256 * 65 * 16 <= small < big
     assert big % 256 == 0
     assert lib.ctct_b200_workspace_bytes(4, 16, 9000, 1) == 0  # more contexts than the kernels support
+    # the limit is where one staged pair of lattice rows stops fitting shared memory (CTCT_MAX_U1):
+    # sizes beyond it are refused here, before a forward call could launch half its kernels
+    header = open(os.path.join(ROOT, "include", "ctct_b200.h")).read()
+    max_u1 = int(re.search(r"#define CTCT_MAX_U1 (\d+)", header).group(1))
+    assert lib.ctct_b200_workspace_bytes(1, 4, max_u1, 1) > 0
+    assert lib.ctct_b200_workspace_bytes(1, 4, max_u1 + 1, 1) == 0
+    assert lib.ctct_b200_loss_forward(None, 0, None, None, None, 1, 4, max_u1 + 1, 5, 0, None, None, None, 0, None) != 0
     assert lib.ctct_b200_workspace_bytes(-1, 16, 5, 1) == 0
 
 

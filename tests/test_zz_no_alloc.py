@@ -5,13 +5,15 @@ application owns all GPU memory, a real-time loop that cannot afford the synchro
 allocation implies).  For them the library carries a fixed 32 MiB scratch array in its device
 image.  This file checks, through the C ABI, that the entry point gives the same costs and
 compact gradient as ctct_b200_loss_forward with a caller-provided workspace, on two calls in a
-row (the second call finds the first call's leftovers in the shared array), and that a problem
-too large for the array is refused.  It is named so that pytest collects it last.
+row (the second call finds the first call's leftovers in the shared array), that both agree with
+the CPU oracle, and that a problem too large for the array is refused.  It is named so that
+pytest collects it last.
 """
 import numpy as np
 import pytest
 import torch
 
+import oracle
 from util import make_case
 
 DEV = "cuda:0"
@@ -47,11 +49,16 @@ def test_noalloc_forward_matches_workspace_forward_twice_in_a_row():
     for lp, ys, lx, ly in cases:
         lp_t, ys_t, lx_t, ly_t = [torch.from_numpy(np.ascontiguousarray(a)).to(DEV) for a in (lp, ys, lx, ly)]
         c_ref, g_ref = _forward(lib, "loss_forward", lp_t, ys_t, lx_t, ly_t, with_workspace=True)
+        # the CPU oracle on the same inputs (float64 evaluation of the reference's formulas)
+        c64, g64 = oracle.ctct_fwd(oracle.collect_units(lp, ys), ys, lx, ly, True, np.float64)
         for attempt in range(2):
             c, g = _forward(lib, "loss_forward_noalloc", lp_t, ys_t, lx_t, ly_t, with_workspace=False)
             assert np.isfinite(c_ref).all()
             np.testing.assert_allclose(c, c_ref, rtol=1e-5, err_msg=f"call {attempt}")
             assert np.abs(g - g_ref).max() < 1e-4, attempt
+            np.testing.assert_allclose(c, c64, rtol=1e-5, err_msg=f"call {attempt} against the oracle")
+            assert np.abs(g[..., :3] - g64).max() < 1e-4, attempt
+            assert not g[..., 3].any()
     # a problem whose workspace exceeds the built-in array is refused before any launch
     N, T, U1, V = 64, 400, 101, 8
     assert lib.ctct_b200_workspace_bytes(N, T, U1, 1) > 32 << 20

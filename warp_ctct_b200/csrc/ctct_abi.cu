@@ -78,8 +78,21 @@ int sm_count() {
 struct LatCfg {
     int C, threads;
 };
+constexpr size_t kLatticeSmemLimit = 220 * 1024;
+// Frames staged per chunk (F) and dynamic shared memory of a lattice CTA: two buffers of F rows of
+// 16-byte records plus the exchange area between warps.
+size_t lattice_smem(int64_t U1, int *F_out) {
+    const size_t rowbytes = static_cast<size_t>(U1) * sizeof(float4);
+    int F = static_cast<int>((48 * 1024) / rowbytes);
+    const int fmax = 16;
+    F = F < 1 ? 1 : (F > fmax ? fmax : F);
+    if (F > 1) F &= ~1;  // even, so that the frame parity is the same in every chunk
+    if (F_out) *F_out = F;
+    return 2 * static_cast<size_t>(F) * rowbytes + 5 * 33 * sizeof(float);
+}
+// Largest U+1 the lattice takes: one staged row pair must fit the shared memory of a CTA.
 bool lattice_config(int64_t U1, LatCfg *cfg) {
-    if (U1 < 1 || U1 > 8192) return false;
+    if (U1 < 1 || U1 > CTCT_MAX_U1 || lattice_smem(U1, nullptr) > kLatticeSmemLimit) return false;
     const int64_t slots = 2 * U1;
     if (slots <= 32) {
         cfg->C = 1;
@@ -179,15 +192,11 @@ int launch_lattice_inst(const LatticeArgs &a, unsigned grid, int block, size_t s
 // `clear`: optional slice that extra blocks of the same launch fill with zeros
 int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st, ClearSlice clear = kNoClear) {
     if (N == 0) return CTCT_OK;
-    const size_t rowbytes = static_cast<size_t>(a.U1) * sizeof(float4);
-    int F = static_cast<int>((48 * 1024) / rowbytes);
-    const int fmax = 16;
-    F = F < 1 ? 1 : (F > fmax ? fmax : F);
-    if (F > 1) F &= ~1;  // even, so that the frame parity is the same in every chunk
+    int F = 1;
+    size_t smem = lattice_smem(a.U1, &F);
     a.F = F;
-    size_t smem = 2 * static_cast<size_t>(F) * rowbytes + 5 * 33 * sizeof(float);
     if (clear.ptr && smem < CLEAR_TILE_BYTES) smem = CLEAR_TILE_BYTES;  // room for the clearing blocks' zero tile
-    if (smem > 220 * 1024) return CTCT_ERR_UNSUPPORTED;
+    if (smem > kLatticeSmemLimit) return CTCT_ERR_UNSUPPORTED;  // lattice_config refuses these sizes up front
     a.smem_bytes = static_cast<unsigned>(smem);
     a.threads = cfg.threads;
     const unsigned own = static_cast<unsigned>(N) * (a.beta_only ? 1 : 2);
@@ -741,6 +750,11 @@ size_t ctct_b200_log_matmul_tc_workspace_bytes(int64_t B, int64_t M, int64_t N, 
     return tc_layout(B, M, N, K).total;
 }
 
+size_t ctct_b200_log_matmul_tc_flags_offset(int64_t B, int64_t M, int64_t N, int64_t K) {
+    if (!tc_shape_ok(B, M, N, K)) return 0;
+    return tc_layout(B, M, N, K).flags;
+}
+
 int ctct_b200_log_matmul_tc(const float *f, const float *g, int64_t B, int64_t M, int64_t N, int64_t K, float *den,
                             void *workspace, size_t workspace_bytes, void *stream) {
     if (!tc_shape_ok(B, M, N, K)) return CTCT_ERR_UNSUPPORTED;
@@ -770,10 +784,9 @@ int ctct_b200_log_matmul_tc(const float *f, const float *g, int64_t B, int64_t M
     rc = check_launch("exp_split g");
     if (rc) return rc;
     prof_mark(slot, 1, st);
-    static std::once_flag attr_once;
-    std::call_once(attr_once, [] {
-        cudaFuncSetAttribute(k_logmm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
-    });
+    // the attribute belongs to the current device, so it is set on every launch (as for the lattice)
+    if (cudaFuncSetAttribute(k_logmm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES) != cudaSuccess)
+        return check_launch("log_matmul_tc smem attribute");
     LogmmTcArgs a;
     a.den = den;
     a.mf = mf;
@@ -888,15 +901,6 @@ static int den_backward_tc(const float4 *g4, const float *gout, const float *gra
     launch_pdl(k_den_weights, dim3(static_cast<unsigned>(N * T)), dim3(128), 0, st, w);
     int rc = check_launch("den_weights");
     if (rc) return rc;
-    static std::once_flag attr_once;
-    std::call_once(attr_once, [] {
-        cudaFuncSetAttribute(k_logmm_bwd_tc<false, false, BW_F_STAGES, BW_F_EBUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             bw_smem_bytes(BW_F_STAGES, BW_F_EBUFS, false));
-        cudaFuncSetAttribute(k_logmm_bwd_tc<false, true, BW_R_STAGES, BW_R_EBUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             bw_smem_bytes(BW_R_STAGES, BW_R_EBUFS, true));
-        cudaFuncSetAttribute(k_logmm_bwd_tc<true, false, BW_G_STAGES, BW_G_EBUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS, false));
-    });
     CUtensorMap m_pk_h, m_pk_l, m_pm_h, m_pm_l, m_f_h, m_f_l, m_g_h, m_g_l;
     if (!make_plane_map(&m_pk_h, ph, N, T, l.Np, BW_BM) || !make_plane_map(&m_pk_l, pl, N, T, l.Np, BW_BM) ||
         !make_plane_map(&m_pm_h, ph, N, T, l.Np, BW_BK) || !make_plane_map(&m_pm_l, pl, N, T, l.Np, BW_BK) ||
@@ -905,12 +909,10 @@ static int den_backward_tc(const float4 *g4, const float *gout, const float *gra
         snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "cuTensorMapEncodeTiled failed");
         return CTCT_ERR_LAUNCH;
     }
-    if (grad_f && grad_g && U1 <= 128 && getenv("CTCT_B200_NO_FUSED_BWD") == nullptr) {
-        // both gradients in one pass over the Ef planes
-        static std::once_flag fused_once;
-        std::call_once(fused_once, [] {
-            cudaFuncSetAttribute(k_den_bwd_fused, cudaFuncAttributeMaxDynamicSharedMemorySize, FU_SMEM_BYTES);
-        });
+    if (grad_f && grad_g && U1 <= 128) {
+        // both gradients in one pass over the Ef planes (shared-memory attribute: per device, so per launch)
+        if (cudaFuncSetAttribute(k_den_bwd_fused, cudaFuncAttributeMaxDynamicSharedMemorySize, FU_SMEM_BYTES) != cudaSuccess)
+            return check_launch("den_bwd_fused smem attribute");
         CUtensorMap m_out;
         if (!make_f32_tile_map(&m_out, grad_f, N, T, V)) {
             snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "cuTensorMapEncodeTiled failed");
@@ -956,6 +958,16 @@ static int den_backward_tc(const float4 *g4, const float *gout, const float *gra
         a.total_tiles = (int)total;
         a.flags = flags;
         const unsigned grid = (unsigned)(total < sm_count() ? total : sm_count());
+        // shared-memory attributes belong to the current device: set with every launch
+        auto smem_attr = [](auto kernel, int bytes) {
+            return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+        };
+        const bool attr_ok =
+            a_mn ? smem_attr(k_logmm_bwd_tc<true, false, BW_G_STAGES, BW_G_EBUFS>, bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS, false))
+            : (K <= BW_BK * BW_ARES_KB)
+                ? smem_attr(k_logmm_bwd_tc<false, true, BW_R_STAGES, BW_R_EBUFS>, bw_smem_bytes(BW_R_STAGES, BW_R_EBUFS, true))
+                : smem_attr(k_logmm_bwd_tc<false, false, BW_F_STAGES, BW_F_EBUFS>, bw_smem_bytes(BW_F_STAGES, BW_F_EBUFS, false));
+        if (!attr_ok) return check_launch("logmm_bwd_tc smem attribute");
         if (a_mn)
             launch_pdl(k_logmm_bwd_tc<true, false, BW_G_STAGES, BW_G_EBUFS>, dim3(grid), dim3(BW_THREADS),
                        bw_smem_bytes(BW_G_STAGES, BW_G_EBUFS, false), st, pa_h, pa_l, pb_h, pb_l, m_src, m_out, a);
@@ -1173,13 +1185,22 @@ extern "C" int ctct_b200_loss_forward_noalloc(const void *log_probs, int dtype, 
     if (!ws_layout(N, T, U1, want_grad, &w)) return CTCT_ERR_UNSUPPORTED;
     if (w.total > CTCT_NOALLOC_SCRATCH_BYTES) return CTCT_ERR_STATIC_SCRATCH;
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return check_launch("noalloc device");
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        if (check_launch("noalloc device") == CTCT_OK) snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "noalloc: no current device");
+        return CTCT_ERR_LAUNCH;
+    }
+    if (dev < 0 || dev >= kMaxDevices) return CTCT_ERR_UNSUPPORTED;  // device ordinal beyond the address cache
     void *scratch = nullptr;
     {
         std::lock_guard<std::mutex> lock(g_noalloc_mutex);
         if (!g_noalloc_ptr[dev]) {
             void *p = nullptr;
-            if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return check_launch("noalloc symbol address");
+            if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) {
+                // never report success with nothing launched
+                if (check_launch("noalloc symbol address") == CTCT_OK)
+                    snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "noalloc: cudaGetSymbolAddress returned no address");
+                return CTCT_ERR_LAUNCH;
+            }
             g_noalloc_ptr[dev] = p;
         }
         scratch = g_noalloc_ptr[dev];
