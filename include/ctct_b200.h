@@ -170,6 +170,32 @@ int ctct_b200_loss_backward_patch(const float *grads3, const float *grad, int sc
                                   void *dense, void *stream);
 
 /*
+ * The loss on RAW joint logits: ctct_loss(log_softmax(logits, -1), ...) with the log-softmax fused
+ * into both passes.  Replaces, for a caller that holds logits, the caller's torch.log_softmax, the
+ * gather and .float() of warp_ctct/__init__.py:124-136, ctct_loss_fwd (csrc/binding.cpp:31-100)
+ * and, in the backward pass, CTCTLoss.backward (warp_ctct/__init__.py:31-33), the scatter of the
+ * gather's autograd and log_softmax's backward.
+ *   forward : one streaming read of the valid rows (t < lx[n], u <= ly[n]) yields each row's
+ *             log-sum-exp and the three log-probs the lattice needs; then the lattice and the
+ *             occupancy gradient as in ctct_b200_loss_forward_fused.  grads3 records carry the row's
+ *             log-sum-exp (log2 units) in their fourth word.  Workspace: ctct_b200_workspace_bytes.
+ *             logits must be device memory.  reduction 0 / 1 / 2 as above (`loss` unused for 0).
+ *   backward: grad_logits[n,t,u,:] = G - softmax(logits[n,t,u,:]) * sum(G), G = the row's <= 3
+ *             occupancy-gradient entries scaled by the upstream gradient (`grad`: N floats, or ONE
+ *             float with scalar_grad != 0 and the reduction of the forward call); valid rows are
+ *             read once and written once, padding rows are written as zeros.  `logits` are the
+ *             forward call's, unchanged; grad_logits has their shape and element type.
+ */
+int ctct_b200_logits_forward(const void *logits, int dtype, const int32_t *ys, const int32_t *lx,
+                             const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int want_grad,
+                             int reduction, int average_frames, float norm, float *costs, float *loss,
+                             float *grads3, void *workspace, size_t workspace_bytes, void *stream);
+int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar_grad, int reduction,
+                              int average_frames, float norm, const void *logits, const int32_t *ys,
+                              const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
+                              int dtype, void *grad_logits, void *stream);
+
+/*
  * The gather alone, in the reference's layout: gathered[n,t,u,0..2] =
  * log_probs[n,t,u,{0, ys[n,u-1], ys[n,u]}] converted to float32 (slots without a
  * label read column 0).  Replaces collect_units (ref_ctct.py:223-230) /
@@ -311,7 +337,8 @@ int ctct_b200_log_matmul_backward_tc(const float *grad_out, const float *lhs, co
  * destroyed by _disable; nothing is recorded when profiling is off.
  *   ctct_b200_profile_read: waits for the recorded events, writes for call i
  *     kind[i] (0 forward, 1 backward, 2 zero fill, 3 log_matmul_tc, 4 simple_forward,
- *     5 simple_backward) and ms[4*i .. 4*i+2] = {gather, lattice, fill_grad} (kind 0),
+ *     5 simple_backward, 6 logits_forward: {log-sum-exp + gather, lattice, fill_grad},
+ *     7 logits_backward: {gradient kernel, 0, 0}) and ms[4*i .. 4*i+2] = {gather, lattice, fill_grad} (kind 0),
  *     {dense gradient / patch / zero fill, 0, 0} (kinds 1, 2), {exp + bf16 split of both operands,
  *     tensor-core kernel, exact fix-up} (kind 3), {compose, lattice, fill_grad} (kind 4),
  *     {denominator weights + grad_f GEMM (or the exact kernel), grad_g GEMM + exact fix-up, label

@@ -158,7 +158,7 @@ def test_costs_and_slot_gradients(W, shape, seed, kw, record_property):
     # The float32 restatement of the reference accumulates its own rounding error along T (its
     # table entries are ~ -T*log V, where one float32 ulp is ~1e-4); that error is measured as its
     # distance to the float64 evaluation of the same formulas and added to the 1e-4 bound.  Against
-    # the float64 evaluation the kernels are held to a 2x tighter bound.
+    # the float64 evaluation the kernels are held to a 10x tighter bound.
     own32 = float(np.abs(g32 - g64).max())
     vs32 = float(np.abs(res["grads"] - g32).max())
     vs64 = float(np.abs(res["grads"] - g64).max())
@@ -169,7 +169,7 @@ def test_costs_and_slot_gradients(W, shape, seed, kw, record_property):
     for key, val in (("own32", own32), ("gpu_vs_oracle32", vs32), ("gpu_vs_oracle64", vs64)):
         record_property(key, val)
     assert vs32 < 1e-4 + own32
-    assert vs64 < 5e-5
+    assert vs64 < 1e-5   # the occupancies of a frame are normalised to sum to one: measured <= 8e-6 at T=300..700
     # forward-only call (beta pass alone) gives the same costs
     res2 = _forward_pieces(W, lp, ys, lx, ly, want_grad=False)
     np.testing.assert_array_equal(res2["costs"], res["costs"])

@@ -329,6 +329,7 @@ def ctct_loss_and_grad(log_probs: T, labels: T, frames_lengths: T, labels_length
     return loss, _fused_backward(ctx, seed)
 
 
+from .logits import FusedLogitsCTCTLoss, FusedLogitsCTCTLossReduced, ctct_loss_from_logits  # noqa: E402,F401
 from .simple import (FusedSimpleCTCTLoss, LogMMExp, SimpleCTCTLoss, ctct_loss_simple_fwd,  # noqa: E402,F401
                      log_matmul, log_matmul_backward, log_matmul_tc)
 

@@ -9,6 +9,7 @@
 #include "gather.cuh"
 #include "grad.cuh"
 #include "lattice.cuh"
+#include "logits.cuh"
 #include "simple.cuh"
 #include "logmm_tc.cuh"
 #include "logmm_bwd_tc.cuh"
@@ -270,7 +271,8 @@ int launch_gather(const void *lp, int dtype, const int *ys, const int *lx, const
 
 int launch_fill_grad(const WsLayout &w, char *ws, const int *ys, const int *lx, const int *ly, float *out,
                      int ref_layout, int64_t N, int64_t T, int64_t U1, cudaStream_t st, const float *costs = nullptr,
-                     float *loss_out = nullptr, ReduceSpec red = ReduceSpec{0, 0, 1.0f}, ClearSlice clear = kNoClear) {
+                     float *loss_out = nullptr, ReduceSpec red = ReduceSpec{0, 0, 1.0f}, ClearSlice clear = kNoClear,
+                     int keep_w = 0) {
     if (N == 0) return CTCT_OK;
     if (T == 0) {
         if (loss_out) {
@@ -295,9 +297,9 @@ int launch_fill_grad(const WsLayout &w, char *ws, const int *ys, const int *lx, 
     g.T = (int)T;
     g.U1 = (int)U1;
     g.ref_layout = ref_layout;
-    const int cells = static_cast<int>(T * U1);
-    g.blocks_per_utt = (cells + 255) / 256;
-    const unsigned long long own = static_cast<unsigned long long>(N) * g.blocks_per_utt;
+    g.keep_w = keep_w;
+    g.frames = N * T;
+    const unsigned long long own = static_cast<unsigned long long>((g.frames + 7) / 8);  // one warp per frame
     if (own + clear_blocks(clear) > 0x7fffffffull) return CTCT_ERR_UNSUPPORTED;
     clear.first_block = static_cast<unsigned>(own);
     g.clear = clear;
@@ -460,6 +462,50 @@ int launch_patch_t(const DenseArgs &a, int64_t N, cudaStream_t st) {
     return check_launch("dense_patch");
 }
 
+// grid of the row-per-warp streaming kernels: one resident wave, rows dealt round-robin to its warps
+unsigned row_stream_grid(int64_t rows) {
+    const int64_t want = (rows + 7) / 8;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * LOGITS_BLOCKS_PER_SM;
+    return static_cast<unsigned>(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+template <typename InT>
+int launch_lse_gather_t(LseArgs a, cudaStream_t st) {
+    a.vec = (a.V % Vec16<InT>::E == 0) && (reinterpret_cast<uintptr_t>(a.logits) % 16 == 0);
+    launch_pdl(k_lse_gather<InT>, dim3(row_stream_grid(a.rows)), dim3(256), 0, st, a);
+    return check_launch("lse_gather");
+}
+
+int launch_lse_gather(const void *logits, int dtype, const int *ys, const int *lx, const int *ly, float4 *G, int64_t N,
+                      int64_t T, int64_t U1, int64_t V, cudaStream_t st) {
+    LseArgs a;
+    a.logits = logits;
+    a.ys = ys;
+    a.lx = lx;
+    a.ly = ly;
+    a.G = G;
+    a.T = (int)T;
+    a.U1 = (int)U1;
+    a.V = (int)V;
+    a.rows = N * T * U1;
+    a.vec = 0;
+    if (a.rows == 0) return CTCT_OK;
+    switch (dtype) {
+    case CTCT_F32: return launch_lse_gather_t<float>(a, st);
+    case CTCT_F16: return launch_lse_gather_t<__half>(a, st);
+    case CTCT_BF16: return launch_lse_gather_t<__nv_bfloat16>(a, st);
+    }
+    return CTCT_ERR_ARG;
+}
+
+template <typename T>
+int launch_logits_grad_t(LogitsGradArgs a, cudaStream_t st) {
+    a.vec = (a.V % Vec16<T>::E == 0) && (reinterpret_cast<uintptr_t>(a.logits) % 16 == 0) &&
+            (reinterpret_cast<uintptr_t>(a.out) % 16 == 0);
+    launch_pdl(k_logits_grad<T>, dim3(row_stream_grid(a.rows)), dim3(256), 0, st, a);
+    return check_launch("logits_grad");
+}
+
 int dense_backward(DenseArgs a, int64_t N, int dtype, void *stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
@@ -487,7 +533,7 @@ int dense_backward(DenseArgs a, int64_t N, int dtype, void *stream) {
 int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
                  int64_t T, int64_t U1, int64_t V, int want_grad, float *costs, float *grads3, void *workspace,
                  size_t workspace_bytes, void *stream, float *loss_out, ReduceSpec red, void *clear = nullptr,
-                 size_t clear_bytes = 0) {
+                 size_t clear_bytes = 0, bool from_logits = false) {
     if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
     if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
     if (N == 0) return CTCT_OK;
@@ -502,16 +548,20 @@ int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int3
     ClearSlice cs[3];
     plan_clear(want_grad ? clear : nullptr, clear_bytes, cs, is_pinned_host(log_probs));
     if (!want_grad && clear && clear_bytes) cs[1] = ClearSlice{static_cast<uint4 *>(clear), clear_bytes / 16, static_cast<int>(clear_bytes % 16), 0};
-    cudaEvent_t *slot = prof_slot(0);
+    cudaEvent_t *slot = prof_slot(from_logits ? 6 : 0);
     prof_mark(slot, 0, st);
-    int rc = launch_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float *>(ws + w.G), N, T, U1, V, true, 1, st, cs[0]);
+    int rc;
+    if (from_logits)  // log-softmax fused in: row log-sum-exp and the three picks in one streaming pass
+        rc = launch_lse_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float4 *>(ws + w.G), N, T, U1, V, st);
+    else
+        rc = launch_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float *>(ws + w.G), N, T, U1, V, true, 1, st, cs[0]);
     if (rc) return rc;
     prof_mark(slot, 1, st);
     rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st, cs[1]);
     if (rc) return rc;
     prof_mark(slot, 2, st);
     if (want_grad) {
-        rc = launch_fill_grad(w, ws, ys, lx, ly, grads3, 0, N, T, U1, st, costs, loss_out, red, cs[2]);
+        rc = launch_fill_grad(w, ws, ys, lx, ly, grads3, 0, N, T, U1, st, costs, loss_out, red, cs[2], from_logits ? 1 : 0);
     } else if (loss_out) {
         k_reduce_costs<<<1, 256, 0, st>>>(costs, lx, (int)N, red, loss_out);
         rc = check_launch("reduce_costs");
@@ -666,6 +716,55 @@ int ctct_b200_loss_backward_patch(const float *grads3, const float *grad, int sc
     a.scalar_grad = scalar_grad ? 1 : 0;
     a.red = ReduceSpec{scalar_grad ? reduction : 0, average_frames ? 1 : 0, scalar_grad ? norm : 1.0f};
     return dense_backward(a, N, dtype, stream);
+}
+
+int ctct_b200_logits_forward(const void *logits, int dtype, const int32_t *ys, const int32_t *lx, const int32_t *ly,
+                             int64_t N, int64_t T, int64_t U1, int64_t V, int want_grad, int reduction,
+                             int average_frames, float norm, float *costs, float *loss, float *grads3, void *workspace,
+                             size_t workspace_bytes, void *stream) {
+    if (reduction < 0 || reduction > 2) return CTCT_ERR_ARG;
+    if (reduction != 0 && (!loss || !(norm > 0.0f))) return CTCT_ERR_ARG;
+    if (logits && is_pinned_host(logits)) return CTCT_ERR_ARG;  // every row is read in full: device memory only
+    return forward_impl(logits, dtype, ys, lx, ly, N, T, U1, V, want_grad, costs, grads3, workspace, workspace_bytes, stream,
+                        reduction ? loss : nullptr, ReduceSpec{reduction, average_frames ? 1 : 0, reduction ? norm : 1.0f},
+                        nullptr, 0, true);
+}
+
+int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar_grad, int reduction, int average_frames,
+                              float norm, const void *logits, const int32_t *ys, const int32_t *lx, const int32_t *ly,
+                              int64_t N, int64_t T, int64_t U1, int64_t V, int dtype, void *grad_logits, void *stream) {
+    if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
+    if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
+    if (scalar_grad && ((reduction != 1 && reduction != 2) || !(norm > 0.0f))) return CTCT_ERR_ARG;
+    if (N == 0 || T == 0) return CTCT_OK;
+    if (!grads3 || !grad || !logits || !lx || !ly || !grad_logits || (U1 > 1 && !ys)) return CTCT_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(grads3) % 16) return CTCT_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LogitsGradArgs a;
+    a.logits = logits;
+    a.GR = reinterpret_cast<const float4 *>(grads3);
+    a.grad_out = grad;
+    a.ys = ys;
+    a.lx = lx;
+    a.ly = ly;
+    a.out = grad_logits;
+    a.T = (int)T;
+    a.U1 = (int)U1;
+    a.V = (int)V;
+    a.vec = 0;
+    a.scalar_grad = scalar_grad ? 1 : 0;
+    a.red = ReduceSpec{scalar_grad ? reduction : 0, average_frames ? 1 : 0, scalar_grad ? norm : 1.0f};
+    a.rows = N * T * U1;
+    cudaEvent_t *slot = prof_slot(7);
+    prof_mark(slot, 0, st);
+    int rc = CTCT_ERR_ARG;
+    switch (dtype) {
+    case CTCT_F32: rc = launch_logits_grad_t<float>(a, st); break;
+    case CTCT_F16: rc = launch_logits_grad_t<__half>(a, st); break;
+    case CTCT_BF16: rc = launch_logits_grad_t<__nv_bfloat16>(a, st); break;
+    }
+    prof_mark(slot, 1, st);
+    return rc;
 }
 
 int ctct_b200_gather(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx, const int32_t *ly,
@@ -1148,7 +1247,7 @@ int ctct_b200_profile_read(float *ms, int *kind, int capacity) {
     for (int i = 0; i < n; ++i) {
         cudaEvent_t *e = g_prof.ev + 4 * i;
         const int k_ = g_prof.kind[i];
-        const int pairs = (k_ == 0 || k_ >= 3) ? 3 : 1;  // intervals recorded per kind
+        const int pairs = (k_ == 0 || (k_ >= 3 && k_ <= 6)) ? 3 : 1;  // intervals recorded per kind
         if (cudaEventSynchronize(e[pairs]) != cudaSuccess) return check_launch("profile sync");
         kind[i] = g_prof.kind[i];
         for (int k = 0; k < 3; ++k) {

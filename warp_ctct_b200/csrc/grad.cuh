@@ -95,51 +95,88 @@ struct GradArgs {
     const float *llf;   // [N][2]
     const int *lli;     // [N][2]
     const int *ys, *lx, *ly;
-    float *out;         // internal [N][T][U1] float4 {g0,g1,g2,0} or reference [N][T][U1][3]
+    float *out;         // internal [N][T][U1] float4 {g0,g1,g2,w} or reference [N][T][U1][3]
     int T, U1;
     int ref_layout;
-    // optional fused reduction of the costs (done by block (0,0)); loss_out == nullptr: none
+    int keep_w;         // internal layout: copy the fourth word of the G record (a row's log-sum-exp) into w, else w = 0
+    // optional fused reduction of the costs (done by block 0); loss_out == nullptr: none
     const float *costs;
     float *loss_out;
     int N;
     ReduceSpec red;
-    int blocks_per_utt;  // own blocks: N * blocks_per_utt, utterance n = block / blocks_per_utt
+    int64_t frames;     // N * T: own blocks = ceil(frames / 8), one warp per frame
     ClearSlice clear;
 };
 
-// One thread per (t,u) of one utterance.  Every arc (state at t) -> (state at
-// t+1) contributes exp2(alpha + logp + beta - loglik); arcs outside the band contribute an
-// exact 0 because one of the two variables is "impossible" there, so the reference's band
-// guards (gather.cu:335-337,355-359) need no restating.
+// One warp per frame (n,t); lanes stride over the contexts u.  Every arc (state at t) -> (state at
+// t+1) contributes exp2(alpha + logp + beta - loglik); arcs outside the band contribute an exact 0
+// because one of the two variables is "impossible" there, so the reference's band guards
+// (gather.cu:335-337,355-359) need no restating.
+//
+// Exactly one arc leaves every frame on every alignment, so the occupancies of a frame sum to one.
+// The warp divides by the sum it actually gets: what alpha, beta and the log-likelihood have each
+// accumulated in approximation error over up to T recursion steps is common to all arcs of the frame
+// and cancels, which leaves the relative error of single terms (~1e-6) instead of ~1e-7 per step
+// times T.  The first FG_KEEP * 32 contexts stay in registers between the two passes; beyond that
+// (U+1 > 128) the occupancies are evaluated a second time from L1/L2.
+constexpr int FG_KEEP = 4;
 __global__ void __launch_bounds__(256) k_fill_grad(const GradArgs a) {
     pdl_wait();
     if (clear_role(a.clear, nullptr, 0)) return;
     if (a.loss_out != nullptr && blockIdx.x == 0) reduce_costs_block(a.costs, a.lx, a.N, a.red, a.loss_out);
-    const int n = blockIdx.x / a.blocks_per_utt;
-    const int cells = a.T * a.U1;
-    const int idx = (blockIdx.x - n * a.blocks_per_utt) * blockDim.x + threadIdx.x;
-    if (idx >= cells) return;
-    const int t = idx / a.U1;
-    const int u = idx - t * a.U1;
-    const int U = a.U1 - 1;
+    const int lane = threadIdx.x & 31;
+    const int64_t nt = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (nt >= a.frames) return;
+    const int n = static_cast<int>(nt / a.T);
+    const int t = static_cast<int>(nt - static_cast<int64_t>(n) * a.T);
+    const int U1 = a.U1, U = U1 - 1;
     const int Tn = max(0, min(a.lx[n], a.T));
     const int Un = max(0, min(a.ly[n], U));
-    const int64_t nt = static_cast<int64_t>(n) * a.T + t;
-
-    float3 g = make_float3(0.0f, 0.0f, 0.0f);
     const float lf = a.llf[n * 2 + 1];
-    if (t < Tn && u <= Un && lf > NEG_TEST) {
-        const float3 occ = occupancies(a.G, a.TAB, a.ys + static_cast<int64_t>(n) * U, nt, u, a.U1, Un, lf, a.lli[n * 2 + 1]);
-        g = make_float3(-occ.x, -occ.y, -occ.z);
+    const bool live = t < Tn && lf > NEG_TEST;
+    const int li = a.lli[n * 2 + 1];
+    const int *y = a.ys + static_cast<int64_t>(n) * U;
+
+    float3 keep[FG_KEEP];
+    float z = 0.0f;
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < FG_KEEP; ++i) {
+            const int u = lane + 32 * i;
+            keep[i] = make_float3(0.0f, 0.0f, 0.0f);
+            if (u <= Un) {
+                keep[i] = occupancies(a.G, a.TAB, y, nt, u, U1, Un, lf, li);
+                z += keep[i].x + keep[i].y + keep[i].z;
+            }
+        }
+        for (int u = lane + 32 * FG_KEEP; u <= Un; u += 32) {
+            const float3 o = occupancies(a.G, a.TAB, y, nt, u, U1, Un, lf, li);
+            z += o.x + o.y + o.z;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
     }
-    if (a.ref_layout) {
-        float *o = a.out + (nt * a.U1 + u) * 3;
-        o[0] = g.x;
-        o[1] = g.y;
-        o[2] = g.z;
-    } else {
-        reinterpret_cast<float4 *>(a.out)[nt * a.U1 + u] = make_float4(g.x, g.y, g.z, 0.0f);
+    const float inv = (z > 0.0f) ? -1.0f / z : -1.0f;  // gradient of the cost: minus the occupancy
+
+    auto put = [&](int u, float3 o) {
+        const float3 g = make_float3(o.x * inv, o.y * inv, o.z * inv);
+        if (a.ref_layout) {
+            float *p = a.out + (nt * U1 + u) * 3;
+            p[0] = g.x;
+            p[1] = g.y;
+            p[2] = g.z;
+        } else {
+            const float w = (a.keep_w && live && u <= Un) ? a.G[nt * U1 + u].w : 0.0f;
+            reinterpret_cast<float4 *>(a.out)[nt * U1 + u] = make_float4(g.x, g.y, g.z, w);
+        }
+    };
+#pragma unroll
+    for (int i = 0; i < FG_KEEP; ++i) {
+        const int u = lane + 32 * i;
+        if (u < U1) put(u, (live && u <= Un) ? keep[i] : make_float3(0.0f, 0.0f, 0.0f));
     }
+    for (int u = lane + 32 * FG_KEEP; u < U1; u += 32)
+        put(u, (live && u <= Un) ? occupancies(a.G, a.TAB, y, nt, u, U1, Un, lf, li) : make_float3(0.0f, 0.0f, 0.0f));
 }
 
 // ---------------------------------------------------------------------------------------
