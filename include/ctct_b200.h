@@ -180,6 +180,11 @@ int ctct_b200_loss_backward_patch(const float *grads3, const float *grad, int sc
  *             occupancy gradient as in ctct_b200_loss_forward_fused.  grads3 records carry the row's
  *             log-sum-exp (log2 units) in their fourth word.  Workspace: ctct_b200_workspace_bytes.
  *             logits must be device memory.  reduction 0 / 1 / 2 as above (`loss` unused for 0).
+ *             grad_logits (optional, NULL = none; needs V * sizeof(element) % 16 == 0 and a 16-byte
+ *             aligned base): the buffer the backward call will write.  Its padding rows (t >= lx[n]
+ *             or u > ly[n]; 30-70 % of the tensor for ragged batches) are zero-filled by extra thread
+ *             blocks of the latency-bound lattice launch, so that the backward call, given
+ *             padding_cleared = 1, only touches the valid rows.
  *   backward: grad_logits[n,t,u,:] = G - softmax(logits[n,t,u,:]) * sum(G), G = the row's <= 3
  *             occupancy-gradient entries scaled by the upstream gradient (`grad`: N floats, or ONE
  *             float with scalar_grad != 0 and the reduction of the forward call); valid rows are
@@ -189,11 +194,12 @@ int ctct_b200_loss_backward_patch(const float *grads3, const float *grad, int sc
 int ctct_b200_logits_forward(const void *logits, int dtype, const int32_t *ys, const int32_t *lx,
                              const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int want_grad,
                              int reduction, int average_frames, float norm, float *costs, float *loss,
-                             float *grads3, void *workspace, size_t workspace_bytes, void *stream);
+                             float *grads3, void *grad_logits, void *workspace, size_t workspace_bytes,
+                             void *stream);
 int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar_grad, int reduction,
                               int average_frames, float norm, const void *logits, const int32_t *ys,
                               const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
-                              int dtype, void *grad_logits, void *stream);
+                              int dtype, void *grad_logits, int padding_cleared, void *stream);
 
 /*
  * The gather alone, in the reference's layout: gathered[n,t,u,0..2] =
@@ -206,6 +212,17 @@ int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar
 int ctct_b200_gather(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx,
                      const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int valid_only,
                      float *gathered, void *stream);
+
+/*
+ * Benchmark hook (no counterpart in the reference): the forward pass's gather alone on a float32
+ * joint tensor, valid rows only, written as 16-byte records {blank, repeat, next, 0} in log2 units
+ * (N*T*U1*4 floats), with `per` (1, 2, 4, 8 or 16) independent loads in flight per thread and
+ * `blocks_per_sm` blocks of 256 threads per SM (0 = one thread per `per` elements).  Used to measure
+ * how many isolated DRAM reads per second the GPU sustains.
+ */
+int ctct_b200_gather_probe(const float *log_probs, const int32_t *ys, const int32_t *lx, const int32_t *ly,
+                           int64_t N, int64_t T, int64_t U1, int64_t V, int per, int blocks_per_sm,
+                           float *records, void *stream);
 
 /*
  * Forward from pre-gathered log-probs, the reference's extension entry point

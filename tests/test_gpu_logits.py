@@ -174,3 +174,44 @@ def test_benchmark_shape_from_logits(W):
         err = np.abs(grad[n].cpu().numpy() - d_ref[0]).max() * N
         print(f"\nutterance {n}: max |grad - oracle64| (per unit of upstream gradient) = {err:.2e}")
         assert err < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_padding_cleared_in_the_forward_pass_gives_the_same_gradient(W, dtype, monkeypatch):
+    """With the gradient buffer allocated by the forward pass, extra blocks of the lattice launch zero
+    its padding rows and the backward kernel writes valid rows only; without, the backward kernel
+    writes everything.  Same bits either way, also for a second backward through a retained graph."""
+    N, T, U1, V = 5, 37, 12, 72
+    _, ys, lx, ly = make_case(N, T, U1, V, 1.0, 91, lx_range=(10, 37), ly_range=(1, 11), repeat_prob=0.2)
+    lx[1], ly[2] = 37, 11
+    rng = np.random.default_rng(91)
+    x = torch.from_numpy(rng.standard_normal((N, T, U1, V)).astype(np.float32)).to(dtype)
+    ys_t, lx_t, ly_t = _dev(ys, lx, ly)
+    go = torch.tensor([0.5, 2.0, 1.25, 1.0, 0.75], device=DEV)
+    grads = {}
+    for mode in ("one_pass", "padding_precleared"):
+        monkeypatch.setattr(W, "PREZERO", mode == "padding_precleared")
+        monkeypatch.setattr(W, "PREZERO_MIN_BYTES", 0)
+        for red in ("none", "mean"):
+            x_t = x.to(DEV).requires_grad_(True)
+            loss = W.ctct_loss_from_logits(x_t, ys_t, lx_t, ly_t, reduction=red, average_frames=True)
+            if red == "none":
+                # poison what the allocator hands out next, so that stale bytes cannot pass for zeros
+                junk = torch.full_like(x_t, 7.0)
+                del junk
+                loss.backward(go, retain_graph=True)
+                first = x_t.grad.clone()
+                x_t.grad = None
+                loss.backward(go)
+                assert torch.equal(first, x_t.grad)
+            else:
+                loss.backward()
+            grads[(mode, red)] = x_t.grad.clone()
+    for red in ("none", "mean"):
+        assert torch.equal(grads[("one_pass", red)], grads[("padding_precleared", red)]), red
+    _, d_ref = oracle_from_logits(x.float().numpy(), ys, lx, ly, go.cpu().numpy() / lx)
+    got = grads[("padding_precleared", "none")].float().cpu().numpy()
+    tol = 1e-4 if dtype == torch.float32 else 2e-3
+    assert np.abs(got - d_ref).max() < tol
+    for n in range(N):
+        assert not got[n, lx[n]:].any() and not got[n, :, ly[n] + 1:].any()

@@ -162,3 +162,27 @@ def test_simple_loss_equals_standard_loss_on_composed_joint():
     np.testing.assert_allclose(c_u, c_j, rtol=1e-5)
     np.testing.assert_allclose(gfu, d_j.astype(np.float64).sum(2), atol=2e-5)
     np.testing.assert_allclose(ggu, d_j.astype(np.float64).sum(1), atol=2e-5)
+
+
+def test_python_restatement_matches_reference_outputs(golden):
+    """oracle/ref_py.py (per-cell Python loops, the reference's own style of CPU code; timed by the
+    benchmark) against the reference's log-likelihoods and the C oracle's gradient."""
+    import torch
+    from oracle import ref_py
+    for name in _cases(golden):
+        lp, ys = golden[f"{name}/lp"].astype(np.float32), golden[f"{name}/ys"]
+        T, U1, V = lp.shape
+        if T * U1 > 400:
+            continue
+        cost, grad = ref_py.loss_and_gradient(lp, ys)
+        want = -float(golden[f"{name}/bw_shift_ll"])
+        assert abs(cost - want) <= 2e-6 * max(1.0, abs(want)), name
+        _, a_ll = ref_py.forward_variables(torch.from_numpy(lp), torch.from_numpy(ys))
+        assert abs(float(a_ll) - float(golden[f"{name}/fw_simple_ll"])) <= 2e-6 * max(1.0, abs(want)), name
+        g3 = oracle.collect_units(lp[None], ys[None])
+        _, g64 = oracle.ctct_fwd(g3, ys[None], [T], [U1 - 1], True, np.float64)
+        np.testing.assert_allclose(grad.numpy(), g64[0], atol=2e-5, err_msg=name)
+    # worker-process timing interface used by the benchmark (one process, tiny case)
+    lp, ys = golden["cfg1_0/lp"].astype(np.float32), golden["cfg1_0/ys"]
+    t = ref_py.time_utterances(lp[None], ys[None], [lp.shape[0]], [lp.shape[1] - 1], processes=1)
+    assert len(t) == 1 and t[0] > 0

@@ -10,7 +10,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from warp_ctct_b200.sharded import plan_shards, reduce_costs, shard_weights
+from warp_ctct_b200 import sharded
+from warp_ctct_b200.sharded import PendingLoss, plan_shards, reduce_costs, shard_weights
 
 
 def _lengths(seed, G, lxr=(100, 400), lyr=(10, 100)):
@@ -72,6 +73,23 @@ def _worker(rank, world, port, out):
                                    torch.allclose(c.grad, scale.float(), rtol=1e-6))
         c = all_costs[mine].clone().requires_grad_(True)
         res["none"] = (torch.equal(reduce_costs(c, lx[mine], G, "none", False), c), True)
+        # the all-reduce is asynchronous: backward() and metadata queries leave it in flight, the
+        # first read of the value settles it
+        c = all_costs[mine].clone().requires_grad_(True)
+        loss = reduce_costs(c, lx[mine], G, "sum", False)
+        pending = isinstance(loss, PendingLoss) and loss._work is not None
+        shape_ok = loss.shape == () and loss.requires_grad and loss.dim() == 0
+        still = loss._work is not None
+        loss.backward()
+        after_backward = loss._work is not None and torch.allclose(c.grad, torch.ones(len(mine)))
+        doubled = loss * 2            # arithmetic reads the value: settles, returns a plain tensor
+        settled = loss._work is None and type(doubled) is torch.Tensor
+        value_ok = abs(doubled.item() - 2 * all_costs.sum().item()) < 1e-4 and abs(float(loss) - all_costs.sum().item()) < 1e-4
+        res["pending"] = (pending and shape_ok and still and after_backward, settled and value_ok)
+        # never more than a handful in flight: older ones are settled as new ones start
+        keep = [reduce_costs(all_costs[mine].clone(), lx[mine], G, "mean", False) for _ in range(10)]
+        in_flight = sum(1 for k in keep if k._work is not None)
+        res["bounded"] = (in_flight <= sharded._MAX_INFLIGHT, all(abs(k.item() - all_costs.mean().item()) < 1e-5 for k in keep))
         out[rank] = res
     finally:
         dist.destroy_process_group()

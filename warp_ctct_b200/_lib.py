@@ -39,10 +39,11 @@ SIGNATURES = {
     "ctct_b200_loss_backward_patch": (_int, [_vp, _vp, _int, _int, _int, C.c_float, _vp, _vp, _vp, _i64, _i64, _i64,
                                              _i64, _int, _vp, _vp]),
     "ctct_b200_logits_forward": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int, _int, C.c_float,
-                                        _vp, _vp, _vp, _vp, _sz, _vp]),
+                                        _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "ctct_b200_logits_backward": (_int, [_vp, _vp, _int, _int, _int, C.c_float, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
-                                         _i64, _int, _vp, _vp]),
+                                         _i64, _int, _vp, _int, _vp]),
     "ctct_b200_gather": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
+    "ctct_b200_gather_probe": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp, _vp]),
     "ctct_b200_gathered_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
     "ctct_b200_export_tables": (_int, [_vp, _sz, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "ctct_b200_log_matmul": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),

@@ -170,4 +170,50 @@ __device__ __forceinline__ bool clear_role(const ClearSlice &c, void *smem, unsi
     return true;
 }
 
+// Ragged variant: extra blocks of a launch zero the PADDING ROWS of an (N,T,U1,V) tensor, i.e. for every
+// (n,t) slab the contiguous block of rows u > ly[n] (the whole slab when t >= lx[n]).  Block
+// first_block + s handles slab s.  The loss on raw logits uses it to move the zero half of its dense
+// gradient under the latency-bound lattice.  row_bytes must be a multiple of 16, `out` 16-byte aligned.
+struct PadClear {
+    unsigned char *out;        // nullptr: none
+    const int *lx, *ly;
+    int T, U1;
+    unsigned row_bytes;        // V * sizeof(element)
+    unsigned first_block;
+    unsigned slabs;            // N * T
+};
+
+// Returns true if this block is a padding-clearing block (and has done its work).  `smem`: at least
+// CLEAR_TILE_BYTES, 16-byte aligned.
+__device__ __forceinline__ bool pad_clear_role(const PadClear &c, void *smem) {
+    if (c.out == nullptr || blockIdx.x < c.first_block) return false;
+    const unsigned slab = blockIdx.x - c.first_block;
+    if (slab >= c.slabs) return true;
+    const int n = static_cast<int>(slab / static_cast<unsigned>(c.T));
+    const int t = static_cast<int>(slab - static_cast<unsigned>(n) * c.T);
+    const int Un = (t < c.lx[n]) ? min(c.ly[n], c.U1 - 1) : -1;
+    const unsigned long long bytes = static_cast<unsigned long long>(c.U1 - 1 - Un) * c.row_bytes;
+    if (bytes == 0) return true;
+    unsigned char *p = c.out + (static_cast<unsigned long long>(slab) * c.U1 + (Un + 1)) * c.row_bytes;
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    uint4 *tile = static_cast<uint4 *>(smem);
+    for (unsigned i = threadIdx.x; i < CLEAR_TILE_BYTES / 16; i += blockDim.x) tile[i] = z;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> async proxy reads
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned src = static_cast<unsigned>(__cvta_generic_to_shared(tile));
+        unsigned long long done = 0;
+        while (done < bytes) {
+            const unsigned long long left = bytes - done;
+            const unsigned v = left < CLEAR_TILE_BYTES ? static_cast<unsigned>(left) : CLEAR_TILE_BYTES;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(p + done), "r"(src), "r"(v)
+                         : "memory");
+            done += v;
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the tile must outlive the reads
+    }
+    return true;
+}
+
 }  // namespace ctct

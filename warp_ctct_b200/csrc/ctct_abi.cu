@@ -140,6 +140,7 @@ bool dims_ok(int64_t N, int64_t T, int64_t U1) {
 }
 
 const ClearSlice kNoClear = {nullptr, 0, 0, 0};
+const PadClear kNoPad = {nullptr, nullptr, nullptr, 0, 0, 0, 0, 0};
 
 // number of clearing blocks a slice adds to a launch
 unsigned clear_blocks(const ClearSlice &c) {
@@ -191,19 +192,23 @@ int launch_lattice_inst(const LatticeArgs &a, unsigned grid, int block, size_t s
 }
 
 // `clear`: optional slice that extra blocks of the same launch fill with zeros
-int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st, ClearSlice clear = kNoClear) {
+int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st, ClearSlice clear = kNoClear,
+                   PadClear pad = kNoPad) {
     if (N == 0) return CTCT_OK;
     int F = 1;
     size_t smem = lattice_smem(a.U1, &F);
     a.F = F;
-    if (clear.ptr && smem < CLEAR_TILE_BYTES) smem = CLEAR_TILE_BYTES;  // room for the clearing blocks' zero tile
+    if (pad.out) clear = kNoClear;  // one kind of clearing per launch
+    if ((clear.ptr || pad.out) && smem < CLEAR_TILE_BYTES) smem = CLEAR_TILE_BYTES;  // room for the clearing blocks' zero tile
     if (smem > kLatticeSmemLimit) return CTCT_ERR_UNSUPPORTED;  // lattice_config refuses these sizes up front
     a.smem_bytes = static_cast<unsigned>(smem);
     a.threads = cfg.threads;
     const unsigned own = static_cast<unsigned>(N) * (a.beta_only ? 1 : 2);
-    const unsigned zero_blocks = clear_blocks(clear);
+    const unsigned zero_blocks = pad.out ? pad.slabs : clear_blocks(clear);
     clear.first_block = own;
     a.clear = clear;
+    pad.first_block = own;
+    a.pad = pad;
     if (static_cast<unsigned long long>(own) + zero_blocks > 0x7fffffffull) return CTCT_ERR_UNSUPPORTED;
     const unsigned grid = own + zero_blocks;
     const int block = (zero_blocks && cfg.threads < 256) ? 256 : cfg.threads;
@@ -462,17 +467,11 @@ int launch_patch_t(const DenseArgs &a, int64_t N, cudaStream_t st) {
     return check_launch("dense_patch");
 }
 
-// grid of the row-per-warp streaming kernels: one resident wave, rows dealt round-robin to its warps
-unsigned row_stream_grid(int64_t rows) {
-    const int64_t want = (rows + 7) / 8;
-    const int64_t cap = static_cast<int64_t>(sm_count()) * LOGITS_BLOCKS_PER_SM;
-    return static_cast<unsigned>(want < cap ? (want > 0 ? want : 1) : cap);
-}
-
 template <typename InT>
 int launch_lse_gather_t(LseArgs a, cudaStream_t st) {
     a.vec = (a.V % Vec16<InT>::E == 0) && (reinterpret_cast<uintptr_t>(a.logits) % 16 == 0);
-    launch_pdl(k_lse_gather<InT>, dim3(row_stream_grid(a.rows)), dim3(256), 0, st, a);
+    // one block per (n,t) slab; N * T < 2^31 (dims_ok)
+    launch_pdl(k_lse_gather<InT>, dim3(static_cast<unsigned>(a.rows / a.U1)), dim3(256), LSE_SMEM_BYTES, st, a);
     return check_launch("lse_gather");
 }
 
@@ -502,7 +501,7 @@ template <typename T>
 int launch_logits_grad_t(LogitsGradArgs a, cudaStream_t st) {
     a.vec = (a.V % Vec16<T>::E == 0) && (reinterpret_cast<uintptr_t>(a.logits) % 16 == 0) &&
             (reinterpret_cast<uintptr_t>(a.out) % 16 == 0);
-    launch_pdl(k_logits_grad<T>, dim3(row_stream_grid(a.rows)), dim3(256), 0, st, a);
+    launch_pdl(k_logits_grad<T>, dim3(static_cast<unsigned>(a.rows / a.U1)), dim3(256), 0, st, a);
     return check_launch("logits_grad");
 }
 
@@ -546,8 +545,8 @@ int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int3
 
     if (clear && reinterpret_cast<uintptr_t>(clear) % 16) return CTCT_ERR_ARG;
     ClearSlice cs[3];
-    plan_clear(want_grad ? clear : nullptr, clear_bytes, cs, is_pinned_host(log_probs));
-    if (!want_grad && clear && clear_bytes) cs[1] = ClearSlice{static_cast<uint4 *>(clear), clear_bytes / 16, static_cast<int>(clear_bytes % 16), 0};
+    plan_clear((want_grad && !from_logits) ? clear : nullptr, clear_bytes, cs, is_pinned_host(log_probs));
+    if (!want_grad && !from_logits && clear && clear_bytes) cs[1] = ClearSlice{static_cast<uint4 *>(clear), clear_bytes / 16, static_cast<int>(clear_bytes % 16), 0};
     cudaEvent_t *slot = prof_slot(from_logits ? 6 : 0);
     prof_mark(slot, 0, st);
     int rc;
@@ -557,7 +556,19 @@ int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int3
         rc = launch_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float *>(ws + w.G), N, T, U1, V, true, 1, st, cs[0]);
     if (rc) return rc;
     prof_mark(slot, 1, st);
-    rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st, cs[1]);
+    PadClear pad = kNoPad;
+    if (from_logits && clear && want_grad) {  // `clear` is the gradient buffer of the backward pass: zero its padding rows
+        const size_t esize = dtype == CTCT_F32 ? 4 : 2;
+        if ((V * esize) % 16 || clear_bytes != static_cast<size_t>(N) * T * U1 * V * esize) return CTCT_ERR_ARG;
+        pad.out = static_cast<unsigned char *>(clear);
+        pad.lx = lx;
+        pad.ly = ly;
+        pad.T = (int)T;
+        pad.U1 = (int)U1;
+        pad.row_bytes = static_cast<unsigned>(V * esize);
+        pad.slabs = static_cast<unsigned>(N * T);
+    }
+    rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st, cs[1], pad);
     if (rc) return rc;
     prof_mark(slot, 2, st);
     if (want_grad) {
@@ -568,6 +579,23 @@ int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int3
     }
     prof_mark(slot, 3, st);
     return rc;
+}
+
+// Test / benchmark hook: the gather of the forward pass alone (float32 joint tensor, internal record
+// layout) with `per` independent loads in flight per thread and a grid of `blocks_per_sm` blocks per SM
+// (0: as many blocks as the elements need).
+template <int PER>
+int gather_probe_t(const float *lp, const int *ys, const int *lx, const int *ly, float *out, int64_t N, int64_t T,
+                          int64_t U1, int64_t V, int blocks_per_sm, cudaStream_t st) {
+    const int64_t total = N * T * U1 * 4;
+    if (total == 0) return CTCT_OK;
+    if (total >= (int64_t(1) << 31) - int64_t(1 << 22) * PER) return CTCT_ERR_UNSUPPORTED;
+    const int64_t want = (total + 256 * PER - 1) / (256 * PER);
+    const int64_t cap = blocks_per_sm > 0 ? static_cast<int64_t>(sm_count()) * blocks_per_sm : want;
+    const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+    launch_pdl(k_gather3<float, unsigned, true, PER>, dim3(grid), dim3(256), 0, st, lp, ys, lx, ly, out, (int)T, (int)U1, (int)V,
+               (unsigned)total, 1, kNoClear);
+    return check_launch("gather_probe");
 }
 
 }  // namespace
@@ -720,19 +748,22 @@ int ctct_b200_loss_backward_patch(const float *grads3, const float *grad, int sc
 
 int ctct_b200_logits_forward(const void *logits, int dtype, const int32_t *ys, const int32_t *lx, const int32_t *ly,
                              int64_t N, int64_t T, int64_t U1, int64_t V, int want_grad, int reduction,
-                             int average_frames, float norm, float *costs, float *loss, float *grads3, void *workspace,
-                             size_t workspace_bytes, void *stream) {
+                             int average_frames, float norm, float *costs, float *loss, float *grads3,
+                             void *grad_logits, void *workspace, size_t workspace_bytes, void *stream) {
     if (reduction < 0 || reduction > 2) return CTCT_ERR_ARG;
     if (reduction != 0 && (!loss || !(norm > 0.0f))) return CTCT_ERR_ARG;
     if (logits && is_pinned_host(logits)) return CTCT_ERR_ARG;  // every row is read in full: device memory only
+    if (grad_logits && reinterpret_cast<uintptr_t>(grad_logits) % 16) return CTCT_ERR_ARG;
+    const size_t esize = dtype == CTCT_F32 ? 4 : 2;
     return forward_impl(logits, dtype, ys, lx, ly, N, T, U1, V, want_grad, costs, grads3, workspace, workspace_bytes, stream,
                         reduction ? loss : nullptr, ReduceSpec{reduction, average_frames ? 1 : 0, reduction ? norm : 1.0f},
-                        nullptr, 0, true);
+                        grad_logits, grad_logits ? static_cast<size_t>(N) * T * U1 * V * esize : 0, true);
 }
 
 int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar_grad, int reduction, int average_frames,
                               float norm, const void *logits, const int32_t *ys, const int32_t *lx, const int32_t *ly,
-                              int64_t N, int64_t T, int64_t U1, int64_t V, int dtype, void *grad_logits, void *stream) {
+                              int64_t N, int64_t T, int64_t U1, int64_t V, int dtype, void *grad_logits,
+                              int padding_cleared, void *stream) {
     if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
     if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
     if (scalar_grad && ((reduction != 1 && reduction != 2) || !(norm > 0.0f))) return CTCT_ERR_ARG;
@@ -755,6 +786,7 @@ int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar
     a.scalar_grad = scalar_grad ? 1 : 0;
     a.red = ReduceSpec{scalar_grad ? reduction : 0, average_frames ? 1 : 0, scalar_grad ? norm : 1.0f};
     a.rows = N * T * U1;
+    a.padding_cleared = padding_cleared ? 1 : 0;
     cudaEvent_t *slot = prof_slot(7);
     prof_mark(slot, 0, st);
     int rc = CTCT_ERR_ARG;
@@ -774,6 +806,21 @@ int ctct_b200_gather(const void *log_probs, int dtype, const int32_t *ys, const 
     if (!log_probs || !gathered || (U1 > 1 && !ys) || (valid_only && (!lx || !ly))) return CTCT_ERR_ARG;
     return launch_gather(log_probs, dtype, ys, lx, ly, gathered, N, T, U1, V, false, valid_only ? 1 : 0,
                          static_cast<cudaStream_t>(stream));
+}
+
+int ctct_b200_gather_probe(const float *log_probs, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
+                           int64_t T, int64_t U1, int64_t V, int per, int blocks_per_sm, float *records, void *stream) {
+    if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff || blocks_per_sm < 0 || blocks_per_sm > 32) return CTCT_ERR_ARG;
+    if (!log_probs || !lx || !ly || !records || (U1 > 1 && !ys)) return CTCT_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (per) {
+    case 1: return gather_probe_t<1>(log_probs, ys, lx, ly, records, N, T, U1, V, blocks_per_sm, st);
+    case 2: return gather_probe_t<2>(log_probs, ys, lx, ly, records, N, T, U1, V, blocks_per_sm, st);
+    case 4: return gather_probe_t<4>(log_probs, ys, lx, ly, records, N, T, U1, V, blocks_per_sm, st);
+    case 8: return gather_probe_t<8>(log_probs, ys, lx, ly, records, N, T, U1, V, blocks_per_sm, st);
+    case 16: return gather_probe_t<16>(log_probs, ys, lx, ly, records, N, T, U1, V, blocks_per_sm, st);
+    }
+    return CTCT_ERR_ARG;
 }
 
 int ctct_b200_gathered_forward(const float *gathered, const int32_t *ys, const int32_t *lx, const int32_t *ly,

@@ -4,7 +4,7 @@
 // Replaces the index build + torch.gather of the reference (warp_ctct/__init__.py:124-131,
 // CPU twin collect_units in ref_ctct.py:223-230).  One thread per OUTPUT element so that
 // the stores are coalesced; the loads are one 32-byte sector each by nature, so the kernel
-// lives on memory-level parallelism: four independent elements per thread, all loads
+// lives on memory-level parallelism: PER (four) independent elements per thread, all loads
 // issued before the first store.
 #pragma once
 
@@ -16,7 +16,7 @@ namespace ctct {
 //                   converted to log2 units and clamped at NEG; everything outside t < lx,
 //                   u <= ly is written as 0
 // INTERNAL = false: out[n][t][u][slot]    (the reference's (N,T,U+1,3) layout)
-template <typename InT, typename IdxT, bool INTERNAL>
+template <typename InT, typename IdxT, bool INTERNAL, int PER = 4>
 __global__ void __launch_bounds__(256)
 k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__restrict__ lx,
           const int *__restrict__ ly, float *__restrict__ out, int T, int U1, int V,
@@ -26,7 +26,6 @@ k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__r
     pdl_wait();
     pdl_trigger();
     if (clear_role(clear, nullptr, 0)) return;
-    constexpr int PER = 4;
     const int valid_only = mode & 1;    // read only frames t < lx[n] and contexts u <= ly[n]
     const bool remote = (mode & 2) != 0;  // lp is pinned host memory
     const IdxT stride = static_cast<IdxT>(clear.ptr ? clear.first_block : gridDim.x) * blockDim.x;

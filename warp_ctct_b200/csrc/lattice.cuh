@@ -47,6 +47,7 @@ struct LatticeArgs {
     int beta_only;       // 1: only the backward variable (no gradient wanted), no table stores
     int threads;         // threads of one lattice CTA (multiple of 32, <= blockDim.x)
     ClearSlice clear;    // blocks from clear.first_block on zero a slice of the gradient buffer
+    PadClear pad;        // or: blocks from pad.first_block on zero the padding rows of a gradient buffer
     unsigned smem_bytes; // dynamic shared memory of the launch
 };
 
@@ -369,6 +370,7 @@ __global__ void __launch_bounds__(MAXT, MINB) k_lattice(const LatticeArgs a) {
     extern __shared__ __align__(16) float4 smem4[];
     // clearing blocks need nothing from the gather launch before this one and may run beside it
     if (clear_role(a.clear, smem4, a.smem_bytes)) return;
+    if (pad_clear_role(a.pad, smem4)) return;
     if (static_cast<int>(threadIdx.x) >= a.threads) return;
     pdl_wait();  // the gathered log-probs are complete and visible
     const int dir = a.beta_only ? 1 : static_cast<int>(blockIdx.x & 1);

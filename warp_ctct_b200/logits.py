@@ -20,7 +20,7 @@ T = torch.Tensor
 
 
 def _forward(ctx, logits: T, labels: T, lx: T, ly: T, requires_grad: bool, red: int, average_frames: bool, norm: float):
-    from . import _sizes
+    from . import PREZERO, PREZERO_MIN_BYTES, _sizes
     N, Tm, U1, V = logits.shape
     dev = logits.device
     lib = _lib.lib()
@@ -28,15 +28,22 @@ def _forward(ctx, logits: T, labels: T, lx: T, ly: T, requires_grad: bool, red: 
     with torch.cuda.device(dev):
         out = torch.empty((N + 1,), dtype=torch.float32, device=dev)
         buf = torch.empty((g3_bytes + ws_bytes,), dtype=torch.uint8, device=dev)  # [compact gradient | workspace]
+        # The gradient buffer is allocated now so that the lattice launch can zero its padding rows
+        # (nothing the loss computes is needed for that) while the recursion, which is latency-bound, runs.
+        grad = None
+        if (requires_grad and PREZERO and logits.numel() * logits.element_size() >= PREZERO_MIN_BYTES
+                and (V * logits.element_size()) % 16 == 0):
+            grad = torch.empty_like(logits)
         base = buf.data_ptr()
         rc = lib.ctct_b200_logits_forward(
             logits.data_ptr(), _lib.dtype_code(logits.dtype), labels.data_ptr(), lx.data_ptr(), ly.data_ptr(),
             N, Tm, U1, V, int(requires_grad), red, int(average_frames), norm, out.data_ptr() + 4, out.data_ptr(),
-            base if requires_grad else None, base + g3_bytes, ws_bytes, _lib.stream_ptr(dev))
+            base if requires_grad else None, _lib.ptr(grad), base + g3_bytes, ws_bytes, _lib.stream_ptr(dev))
     _lib.check(rc, "ctct_b200_logits_forward")
     if requires_grad:
         ctx.save_for_backward(buf, logits, labels, lx, ly)
         ctx.meta = (N, Tm, U1, V, red, bool(average_frames), float(norm))
+        ctx.cleared = grad
     return out
 
 
@@ -45,11 +52,14 @@ def _backward(ctx, grad: T) -> T:
     N, Tm, U1, V, red, avg, norm = ctx.meta
     dev = logits.device
     go = grad.to(torch.float32).contiguous()
+    out, ctx.cleared = ctx.cleared, None   # a second backward through a retained graph gets a fresh buffer
+    cleared = out is not None
     with torch.cuda.device(dev):
-        out = torch.empty_like(logits)
+        if out is None:
+            out = torch.empty_like(logits)
         rc = _lib.lib().ctct_b200_logits_backward(
             buf.data_ptr(), go.data_ptr(), int(red != 0), red, int(avg), norm, logits.data_ptr(), labels.data_ptr(),
-            lx.data_ptr(), ly.data_ptr(), N, Tm, U1, V, _lib.dtype_code(logits.dtype), out.data_ptr(),
+            lx.data_ptr(), ly.data_ptr(), N, Tm, U1, V, _lib.dtype_code(logits.dtype), out.data_ptr(), int(cleared),
             _lib.stream_ptr(dev))
     _lib.check(rc, "ctct_b200_logits_backward")
     return out

@@ -7,6 +7,7 @@ warp_ctct/__init__.py:138-147 applied to the GLOBAL batch.
 """
 from __future__ import annotations
 
+import collections
 from typing import List, Optional, Sequence
 
 import torch
@@ -41,6 +42,68 @@ def _multi_rank(group) -> bool:
     return dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
 
 
+# ---- the scalar all-reduce, kept off the compute stream -------------------------------------------
+#
+# The backward pass of a shard needs nothing from the other ranks: the gradient scale is the local
+# utterance weight times the upstream gradient.  Only the VALUE of the reduced loss depends on the
+# collective.  So the all-reduce is issued asynchronously (on the communication stream of the
+# process group, ordered after the kernel that produced this rank's share) and the compute stream
+# waits for it only when somebody looks at the value: `loss.item()`, printing, arithmetic on it.
+# `loss.backward()` does not, so the backward kernels of this step and the forward kernels of the
+# next one run while the 4 bytes travel.
+
+_NO_WAIT_NAMES = {"backward", "register_hook", "retain_grad", "size", "dim", "numel", "stride", "is_contiguous",
+                  "requires_grad_", "__get__"}
+
+
+class PendingLoss(torch.Tensor):
+    """The reduced loss of a sharded step whose all-reduce may still be in flight.
+
+    Behaves like the plain 0-dim tensor it wraps.  Any operation that reads the value first makes the
+    current stream wait for the collective (`settle()`, idempotent; costs nothing once the
+    collective is done); `backward()` and metadata queries do not."""
+
+    _work = None
+
+    def settle(self) -> None:
+        work, self._work = self._work, None
+        if work is not None:
+            work.wait()   # stream wait for NCCL; host wait for gloo
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        if getattr(func, "__name__", "") not in _NO_WAIT_NAMES:
+            for a in args:
+                if isinstance(a, PendingLoss):
+                    a.settle()
+                elif isinstance(a, (list, tuple)):
+                    for b in a:
+                        if isinstance(b, PendingLoss):
+                            b.settle()
+        with torch._C.DisableTorchFunctionSubclass():
+            return func(*args, **(kwargs or {}))
+
+
+# Collectives in flight whose buffers must stay alive: (work, tensor).  The oldest is settled when the
+# fifth arrives, by which time it has long completed, so the wait is free and memory is handed back
+# to the allocator only after the communication stream is done with it.
+_inflight: collections.deque = collections.deque()
+_MAX_INFLIGHT = 4
+
+
+def _async_all_reduce(buf: torch.Tensor, group) -> "PendingLoss | torch.Tensor":
+    """Start sum-all-reduce of `buf` in place; returns it as a PendingLoss (or as it is with one rank)."""
+    if not _multi_rank(group):
+        return buf
+    work = dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True)
+    out = buf.as_subclass(PendingLoss)
+    out._work = work
+    _inflight.append(out)
+    while len(_inflight) > _MAX_INFLIGHT:
+        _inflight.popleft().settle()
+    return out
+
+
 class _AllReduceSum(torch.autograd.Function):
     """y = sum over ranks of x.  Each rank back-propagates only through its own term, so the
     backward is the identity (every rank seeds the same global loss with the same grad)."""
@@ -48,8 +111,7 @@ class _AllReduceSum(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: torch.Tensor, group):
         y = x.clone()
-        if _multi_rank(group):
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+        _started.append(_async_all_reduce(y, group))
         return y
 
     @staticmethod
@@ -59,49 +121,87 @@ class _AllReduceSum(torch.autograd.Function):
 
 class _ShardedReducedLoss(torch.autograd.Function):
     """This rank's share of the reduced global loss straight out of the kernels (see
-    FusedCTCTLossReduced), all-reduced in place before autograd ever sees it: one 4-byte
-    collective and no extra kernel.  The backward is local."""
+    FusedCTCTLossReduced), all-reduced in place: one 4-byte collective and no extra kernel.
+    The backward is local and does not wait for the collective."""
 
     @staticmethod
     def forward(ctx, log_probs, labels, lx, ly, requires_grad: bool, mean: bool, average_frames: bool, norm: float,
-                group):
-        loss = _fused_forward(ctx, log_probs, labels, lx, ly, requires_grad, 2 if mean else 1, bool(average_frames),
-                              float(norm))[0]
-        if _multi_rank(group):
-            dist.all_reduce(loss, op=dist.ReduceOp.SUM, group=group)
+                group, from_logits: bool):
+        if from_logits:
+            from .logits import _forward as fwd
+            ctx.from_logits = True
+            loss = fwd(ctx, log_probs, labels, lx, ly, requires_grad, 2 if mean else 1, bool(average_frames), float(norm))[0]
+        else:
+            ctx.from_logits = False
+            loss = _fused_forward(ctx, log_probs, labels, lx, ly, requires_grad, 2 if mean else 1, bool(average_frames),
+                                  float(norm))[0]
+        _started.append(_async_all_reduce(loss, group))
         return loss
 
     @staticmethod
     def backward(ctx, grad_loss):
-        return _fused_backward(ctx, grad_loss), None, None, None, None, None, None, None, None
+        if ctx.from_logits:
+            from .logits import _backward as bwd
+            return bwd(ctx, grad_loss), None, None, None, None, None, None, None, None, None
+        return _fused_backward(ctx, grad_loss), None, None, None, None, None, None, None, None, None
+
+
+# side channel from the forward of the two functions above to their caller: the started collective
+_started: list = []
+
+
+def _attach(out: torch.Tensor) -> torch.Tensor:
+    """`out` is what autograd returned for a tensor whose all-reduce was just started: give it the
+    pending handle (autograd may have wrapped the tensor in a new Python object)."""
+    pending = _started.pop() if _started else None
+    _started.clear()
+    if not isinstance(pending, PendingLoss):
+        return out
+    if out is pending:
+        return out
+    res = out.as_subclass(PendingLoss)
+    res._work, pending._work = pending._work, None
+    # the queue keeps the object that owns the handle
+    for i, q in enumerate(_inflight):
+        if q is pending:
+            _inflight[i] = res
+    return res
 
 
 def all_reduce_sum(x: torch.Tensor, group=None) -> torch.Tensor:
-    return _AllReduceSum.apply(x, group)
+    return _attach(_AllReduceSum.apply(x, group))
 
 
 def reduce_costs(costs: torch.Tensor, frames_lengths: torch.Tensor, global_batch: int, reduction: Optional[str],
                  average_frames: bool, group=None) -> torch.Tensor:
-    """Reduction of warp_ctct/__init__.py:138-147 over the global batch from this rank's costs."""
+    """Reduction of warp_ctct/__init__.py:138-147 over the global batch from this rank's costs.
+    The division of 'mean' is applied to the local sum, so that the all-reduce is the last operation
+    and nothing on the compute stream waits for it."""
     if average_frames:
         costs = costs / frames_lengths
     if reduction == "none" or reduction is None:
         return costs  # per-utterance costs stay local
-    total = all_reduce_sum(costs.sum(), group)
+    share = costs.sum()
     if reduction == "mean":
-        return total / global_batch
-    return total
+        share = share / global_batch
+    return all_reduce_sum(share, group)
 
 
 def sharded_ctct_loss(log_probs: torch.Tensor, labels: torch.Tensor, frames_lengths: torch.Tensor,
                       labels_lengths: torch.Tensor, global_batch: Optional[int] = None,
-                      reduction: Optional[str] = "mean", average_frames: bool = False, group=None) -> torch.Tensor:
+                      reduction: Optional[str] = "mean", average_frames: bool = False, group=None,
+                      from_logits: bool = False) -> torch.Tensor:
     """``ctct_loss`` on this rank's shard of a batch that is split across the process group.
 
     ``log_probs`` etc. hold only the local utterances.  With ``reduction`` 'mean' or 'sum' the
     returned scalar is the loss of the GLOBAL batch (identical on every rank) and its backward
     writes d(global loss)/d(local log_probs); 'none' returns the local per-utterance costs.
-    ``global_batch`` defaults to the sum of local batch sizes when they are equal on all ranks."""
+    ``global_batch`` defaults to the sum of local batch sizes when they are equal on all ranks.
+    ``from_logits``: ``log_probs`` holds raw scores and the log-softmax is fused into the kernels
+    (``ctct_loss_from_logits``).
+
+    With more than one rank the scalar is a ``PendingLoss``: its all-reduce runs beside the
+    backward pass, and the first operation that reads the value waits for it."""
     assert reduction is None or reduction in ("none", "mean", "sum")
     assert log_probs.dim() == 4 and labels.dim() == 2
     assert log_probs.size(2) == labels.size(1) + 1
@@ -118,11 +218,16 @@ def sharded_ctct_loss(log_probs: torch.Tensor, labels: torch.Tensor, frames_leng
     if reduction in ("mean", "sum") and log_probs.size(0) > 0:
         # this rank's share of the global loss straight out of the kernels (for 'mean' already
         # divided by the global batch); the all-reduce of that one float completes it
-        return _ShardedReducedLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
-                                         enable_grad, reduction == "mean", bool(average_frames), float(global_batch),
-                                         group)
-    costs = FusedCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
-                                enable_grad)
+        return _attach(_ShardedReducedLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths),
+                                                 _as_int(labels_lengths), enable_grad, reduction == "mean",
+                                                 bool(average_frames), float(global_batch), group, bool(from_logits)))
+    if from_logits:
+        from .logits import FusedLogitsCTCTLoss
+        costs = FusedLogitsCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
+                                          enable_grad)
+    else:
+        costs = FusedCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
+                                    enable_grad)
     return reduce_costs(costs, frames_lengths, global_batch, reduction, average_frames, group)
 
 
