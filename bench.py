@@ -53,11 +53,18 @@ UNIT = "utt/s"
 
 
 def base_name(name):
-    return name[:-len("_logits")] if name.endswith("_logits") else name
+    for suffix in ("_packed", "_logits"):
+        if name.endswith(suffix):
+            name = name[:-len(suffix)]
+    return name
 
 
 def is_logits(name):
-    return name.endswith("_logits")
+    return "_logits" in name
+
+
+def is_packed(name):
+    return name.endswith("_packed")
 
 
 def per_gpu_batch(name, world, scaling):
@@ -102,6 +109,8 @@ def make_config(name, world, scaling):
         _, T, U1, V, dt, sigma, lxr, lyr, cap = WORKLOADS[base_name(name)]
         esize = 4 if dt == "f32" else 2
         what = ("ctct_loss_from_logits: raw scores" if is_logits(name) else "ctct_loss: log_softmax of")
+        if is_packed(name):
+            what = "packed layout (valid rows only), " + what
         text = (f"{name}: {what} {sigma}*N(0,1), {dt} fwd+bwd, B={B}/GPU (global {G}), T={T}, U+1={U1}, V={V}, "
                 f"lx~U{list(lxr)}, ly~U{list(lyr)}" + (" capped lx//2" if cap else ""))
         l2 = (f"inputs larger than L2: {B * T * U1 * V * esize / 1e9:.2f} GB joint tensor per GPU and an equally "
@@ -399,6 +408,7 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
     lib = _lib.lib()
     _, T, U1, V, dt, sigma, lxr, lyr, cap = WORKLOADS[base_name(name)]
     logits = is_logits(name)
+    packed = is_packed(name)
     esize = {"f32": 4, "f16": 2}[dt]
     B = per_gpu_batch(name, world, args.scaling)
     G = B * world
@@ -408,14 +418,24 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
     lx, ly, ys = lx_g[mine], ly_g[mine], ys_g[mine]
     assert len(mine) == B
     lp = standard_inputs(name, B, rank, dev)
-    lp.requires_grad_(True)
     ys_t, lx_t, ly_t = (torch.from_numpy(a).to(dev) for a in (ys, lx, ly))
+    if packed:
+        lp = W.pack_joint(lp, lx_t, ly_t).contiguous()
+        torch.cuda.empty_cache()
+    lp.requires_grad_(True)
     steps = args.steps if primary else max(10, min(args.steps, 100))
     n_passes = args.passes if primary else min(args.passes, 3)
 
+    def loss_of(x, y, a, b):
+        if packed:
+            from warp_ctct_b200.sharded import all_reduce_sum
+            return all_reduce_sum(W.ctct_loss_packed(x, y, a, b, reduction="mean", max_frames=T, from_logits=logits,
+                                                     global_batch=G))
+        return sharded_ctct_loss(x, y, a, b, global_batch=G, reduction="mean", from_logits=logits)
+
     def step():
         lp.grad = None
-        loss = sharded_ctct_loss(lp, ys_t, lx_t, ly_t, global_batch=G, reduction="mean", from_logits=logits)
+        loss = loss_of(lp, ys_t, lx_t, ly_t)
         loss.backward()
         return loss
 
@@ -445,16 +465,16 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
     res["profiled_pass_ms_per_step"] = ms_profiled / steps
     peak, peak_kind = peaks()
     rows_valid = int((lx.astype(np.int64) * (ly + 1)).sum())
-    full_bytes = B * T * U1 * V * esize
     valid_bytes = rows_valid * V * esize
-    precleared = (not logits) and bool(W.PREZERO) and full_bytes >= W.PREZERO_MIN_BYTES
+    full_bytes = valid_bytes if packed else B * T * U1 * V * esize   # a packed tensor has no padding rows
+    precleared = (not logits) and (packed or (bool(W.PREZERO) and full_bytes >= W.PREZERO_MIN_BYTES))
     kernels = {}
     if logits:
         k_ms = {"lse_gather": float(fwd[:, 0].mean()), "lattice": float(fwd[:, 1].mean()),
                 "fill_grad": float(fwd[:, 2].mean()), "logits_grad": float(bwd[:, 0].mean())}
         # with the gradient buffer allocated in the forward pass the lattice launch zeroes the padding rows
         # and the backward kernel reads and writes valid rows only; else it also writes the padding
-        pad_cleared = bool(W.PREZERO) and full_bytes >= W.PREZERO_MIN_BYTES and (V * esize) % 16 == 0
+        pad_cleared = (not packed) and bool(W.PREZERO) and full_bytes >= W.PREZERO_MIN_BYTES and (V * esize) % 16 == 0
         bwd_bytes = 2 * valid_bytes if pad_cleared else valid_bytes + full_bytes
         ach = bwd_bytes / (k_ms["logits_grad"] * 1e-3) / 1e9
         fwd_ach = valid_bytes / (k_ms["lse_gather"] * 1e-3) / 1e9
@@ -506,7 +526,7 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
                                   "the dense gradient written once") + f", at the {peak_kind} HBM peak"}
     res["roofline"], res["kernels"] = roofline, kernels
 
-    if primary and precleared:
+    if primary and precleared and not packed:
         # the lattice recursion by itself: a few steps with the clearing moved out of its launch
         W.PREZERO = False
         try:
@@ -527,7 +547,10 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
         # the unfused pipeline on the same logits: torch.log_softmax, this library's ctct_loss, autograd back through both
         def unfused():
             lp.grad = None
-            loss_u = sharded_ctct_loss(lp.log_softmax(-1), ys_t, lx_t, ly_t, global_batch=G, reduction="mean")
+            if packed:
+                loss_u = W.ctct_loss_packed(lp.log_softmax(-1), ys_t, lx_t, ly_t, reduction="mean", max_frames=T, global_batch=G)
+            else:
+                loss_u = sharded_ctct_loss(lp.log_softmax(-1), ys_t, lx_t, ly_t, global_batch=G, reduction="mean")
             loss_u.backward()
             return loss_u
 
@@ -551,7 +574,7 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
             lp_g = lp.detach().requires_grad_(True)   # a fresh leaf: its gradient accumulator belongs to the capturing stream
 
             def graph_step():
-                sharded_ctct_loss(lp_g, ys_t, lx_t, ly_t, global_batch=G, reduction="mean", from_logits=logits).backward()
+                loss_of(lp_g, ys_t, lx_t, ly_t).backward()
 
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -573,12 +596,17 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
             res["cuda_graph_replay_ms_per_step"] = f"not captured: {exc}"
         lp.grad = None
 
+    if args.no_e2e:
+        res["e2e"] = None
+        res["_host"] = (lp.detach().cpu(), ys, lx, ly)
+        return res
+
     # ---- end to end through the public API, inputs in pinned host memory ----
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     tdt = lp.dtype
-    lp_host = torch.empty((B, T, U1, V), dtype=tdt, pin_memory=True)
+    lp_host = torch.empty(tuple(lp.shape), dtype=tdt, pin_memory=True)
     lp_host.copy_(lp.detach())
-    grad_host = torch.empty((B, T, U1, V), dtype=tdt, pin_memory=True)
+    grad_host = torch.empty(tuple(lp.shape), dtype=tdt, pin_memory=True)
     ys_h, lx_h, ly_h = ys_t.cpu().pin_memory(), lx_t.cpu().pin_memory(), ly_t.cpu().pin_memory()
     del lp
     torch.cuda.empty_cache()
@@ -591,14 +619,14 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
     def e2e_full_copy():
         # the whole joint tensor crosses PCIe, then the usual autograd path; the loss is read back
         x, y, a, b = copy_in()
-        loss = sharded_ctct_loss(x, y, a, b, global_batch=G, reduction="mean", from_logits=logits)
+        loss = loss_of(x, y, a, b)
         loss.backward()
         return float(loss.item())
 
     def e2e_full_copy_grad_back():
         # ... and the dense gradient is copied back into pinned host memory as well
         x, y, a, b = copy_in()
-        loss = sharded_ctct_loss(x, y, a, b, global_batch=G, reduction="mean", from_logits=logits)
+        loss = loss_of(x, y, a, b)
         loss.backward()
         grad_host.copy_(x.grad, non_blocking=True)
         return float(loss.item())
@@ -627,14 +655,14 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
                                 "d2h_bytes_per_step": int((lp_host.numel() * esize + 4) * world),
                                 "note": "as full_copy, and the dense gradient copied back to pinned host memory"},
     }
-    if not logits:
+    if not logits and not packed:
         variants["in_place"] = {
             "value": timed_e2e(e2e_in_place), "unit": UNIT,
             "h2d_bytes_per_step": int((rows_valid * 3 * 32 + small) * world), "d2h_bytes_per_step": 4 * world,
             "note": "ctct_loss_and_grad on the joint tensor left in pinned host memory: the gather kernel reads the 3 "
                     "log-probs per valid row in place over PCIe (one 32-byte sector each), labels and lengths are "
                     "copied, the dense gradient stays on the device, the loss scalar is read back"}
-    head = "full_copy" if logits else "in_place"
+    head = "full_copy" if (logits or packed) else "in_place"
     res["e2e"] = {"value": variants[head]["value"], "unit": UNIT,
                   "h2d_bytes_per_step": variants[head]["h2d_bytes_per_step"],
                   "d2h_bytes_per_step": variants[head]["d2h_bytes_per_step"], "steps": e2e_steps, "variant": head,
@@ -677,6 +705,9 @@ def run_b200(args):
         torch.set_num_threads(cores)
         go = np.full((B,), 1.0 / G, np.float32)
         nb = min(B, 32)
+        if is_packed(name):   # the CPU code takes the padded form (it skips padding rows itself)
+            from warp_ctct_b200.packed import unpack_joint
+            lp_host = unpack_joint(lp_host.float(), torch.from_numpy(lx), torch.from_numpy(ly), T, U1)
         xs, yb, lxb, lyb, gob = lp_host[:nb].float(), ys[:nb], lx[:nb], ly[:nb], go[:nb]
         cpu_step_standard(name, xs, yb, lxb, lyb, gob, cores)
         reps, t0 = 3, time.perf_counter()
@@ -1019,11 +1050,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--passes", type=int, default=5, help="timed passes of --steps steps each (median reported)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    choices = sorted(WORKLOADS) + [w + "_logits" for w in sorted(WORKLOADS)] + sorted(SIMPLE_WORKLOADS) + ["gather_probe"]
+    choices = ([w + v for w in sorted(WORKLOADS) for v in ("", "_logits", "_packed", "_logits_packed")]
+               + sorted(SIMPLE_WORKLOADS) + ["gather_probe"])
     ap.add_argument("--workload", default="c2", choices=choices)
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host-resident inputs) measurements")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary c5 measurement of the default workload")
     args = ap.parse_args()
     args.passes = max(1, args.passes)

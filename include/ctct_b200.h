@@ -202,6 +202,44 @@ int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar
                               int dtype, void *grad_logits, int padding_cleared, void *stream);
 
 /*
+ * PACKED (ragged) layout: the joint tensor holds only the valid rows, (rows, V) with
+ * rows = sum_n lx[n] * (ly[n] + 1); utterance n owns rows [cu_rows[n], cu_rows[n+1]), frame-major, ly[n] + 1
+ * rows per frame.  The reference pads every utterance to (T, U+1) and only skips the padding inside
+ * its kernels (csrc/gather.cu:321) while autograd still zero-fills it (warp_ctct/__init__.py:124-131);
+ * here no padding byte is read or written: for ragged batches that is 30-70 % of all traffic.
+ *   ctct_b200_packed_offsets   computes cu_rows (N + 1 int64 on the device) from lx, ly, clamped to T, U1-1
+ *   *_forward_packed / *_backward_packed   as ctct_b200_loss_forward_fused + ctct_b200_loss_backward_patch,
+ *       and as ctct_b200_logits_forward + ctct_b200_logits_backward, on packed tensors.  T and U1 are upper
+ *       bounds of lx and ly + 1 (they size the workspace and grads3 exactly as in the padded calls).
+ *       packed_rows = number of rows of the packed tensor(s); rows an inconsistent lx / ly would place
+ *       beyond it are neither read nor written.  `clear` of the standard-loss forward is the packed
+ *       gradient buffer (packed_rows * V elements), zero-filled by the lattice launch; the backward then
+ *       patches it (pass a buffer cleared with ctct_b200_zero_fill when the forward did not clear it).
+ *       The logits backward writes every row of packed_grad once; nothing needs clearing.
+ */
+int ctct_b200_packed_offsets(const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1,
+                             int64_t *cu_rows, void *stream);
+int ctct_b200_loss_forward_packed(const void *packed, int dtype, const int64_t *cu_rows, int64_t packed_rows,
+                                  const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N, int64_t T,
+                                  int64_t U1, int64_t V, int want_grad, int reduction, int average_frames,
+                                  float norm, float *costs, float *loss, float *grads3, void *clear,
+                                  size_t clear_bytes, void *workspace, size_t workspace_bytes, void *stream);
+int ctct_b200_loss_backward_packed(const float *grads3, const float *grad, int scalar_grad, int reduction,
+                                   int average_frames, float norm, const int64_t *cu_rows, int64_t packed_rows,
+                                   const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N, int64_t T,
+                                   int64_t U1, int64_t V, int dtype, void *packed_grad, void *stream);
+int ctct_b200_logits_forward_packed(const void *packed_logits, int dtype, const int64_t *cu_rows,
+                                    int64_t packed_rows, const int32_t *ys, const int32_t *lx, const int32_t *ly,
+                                    int64_t N, int64_t T, int64_t U1, int64_t V, int want_grad, int reduction,
+                                    int average_frames, float norm, float *costs, float *loss, float *grads3,
+                                    void *workspace, size_t workspace_bytes, void *stream);
+int ctct_b200_logits_backward_packed(const float *grads3, const float *grad, int scalar_grad, int reduction,
+                                     int average_frames, float norm, const void *packed_logits,
+                                     const int64_t *cu_rows, int64_t packed_rows, const int32_t *ys,
+                                     const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1,
+                                     int64_t V, int dtype, void *packed_grad, void *stream);
+
+/*
  * The gather alone, in the reference's layout: gathered[n,t,u,0..2] =
  * log_probs[n,t,u,{0, ys[n,u-1], ys[n,u]}] converted to float32 (slots without a
  * label read column 0).  Replaces collect_units (ref_ctct.py:223-230) /
@@ -306,6 +344,24 @@ int ctct_b200_simple_forward(const float *f, const float *g, const float *den, c
                              const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
                              int want_grad, float *costs, float *grads3, void *workspace,
                              size_t workspace_bytes, void *stream);
+
+/*
+ * The reference's extension entry point for the log-add joiner, ctct_loss_simple_fwd(f, g, ys, den,
+ * lx, ly, requires_grad) of csrc/binding.cpp:103-222 (launchers run_warp_ctct_simple /
+ * run_fill_grad_simple, csrc/core.h:22-37), on PRE-GATHERED operands:
+ *   f (N,T,U1): f[n,t,0] blank, f[n,t,k] = score of label ys[n,k-1];  g (N,U1,3): the three picks of
+ *   every context;  den (N,T,U1) or NULL for the un-normalised loss.  All float32, contiguous.
+ *   costs (N) out; with want_grad also grad_f (N,T,U1), grad_g (N,U1,3) and, when den is given,
+ *   grad_den (N,T,U1): the lattice's occupancy gradient reduced as csrc/binding.cpp:198,209-219 does
+ *   (grad_den = -sum of the three slots, grad_g = sum over t, grad_f[...,0] = sum over u of the blank
+ *   slot, grad_f[...,k] = repeat slot of context k + next slot of context k-1), in fixed order.
+ * Workspace: ctct_b200_simple_gathered_workspace_bytes (256-byte aligned base).
+ */
+size_t ctct_b200_simple_gathered_workspace_bytes(int64_t N, int64_t T, int64_t U1, int want_grad);
+int ctct_b200_simple_gathered_forward(const float *f, const float *g, const float *den, const int32_t *ys,
+                                      const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1,
+                                      int want_grad, float *costs, float *grad_f, float *grad_g,
+                                      float *grad_den, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * Dense gradients of ctct_simple_loss w.r.t. f (N,T,V) and g (N,U1,V), each written once:

@@ -101,3 +101,19 @@ def test_cpu_tensors_are_rejected_like_the_reference():
         W.ctct_loss(lp, ys[:, :1], lens, lens)
     with pytest.raises(AssertionError):
         W.ctct_loss(lp, ys, lens, lens, reduction="avg")
+
+
+def test_import_level_drop_in():
+    """`import warp_ctct` and `warp_ctct._C` resolve to this library with the reference's names."""
+    import warp_ctct
+    import warp_ctct._C as core
+    import warp_ctct_b200 as W
+    assert warp_ctct.ctct_loss is W.ctct_loss and warp_ctct.ctct_simple_loss is W.ctct_simple_loss
+    assert warp_ctct.__all__ == ["ctct_loss", "ctct_simple_loss"] and warp_ctct.__version__ == W.__version__
+    for cls in ("CTCTLoss", "LogMMExp", "SimpleCTCTLoss"):
+        assert getattr(warp_ctct, cls) is getattr(W, cls)
+    for fn in ("ctct_loss_fwd", "ctct_loss_simple_fwd", "log_matmul", "log_matmul_backward"):
+        assert getattr(core, fn) is getattr(W, fn)
+    # the reference's call shape: ctct_loss_simple_fwd(f, g, ys, den, lx, ly, requires_grad)
+    assert list(inspect.signature(core.ctct_loss_simple_fwd).parameters) == ["f", "g", "ys", "den", "lx", "ly", "requires_grad"]
+    assert list(inspect.signature(core.ctct_loss_fwd).parameters) == ["log_probs", "ys", "lx", "ly", "requires_grad"]

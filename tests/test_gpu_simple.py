@@ -331,3 +331,59 @@ def test_simple_loss_tensor_core_edge_shapes(W, shape, lx, ly):
     np.testing.assert_allclose(costs.detach().cpu().numpy(), c_ref, rtol=1e-5)
     np.testing.assert_allclose(f_t.grad.cpu().numpy(), gf_ref, atol=1e-4, rtol=2e-5)
     np.testing.assert_allclose(g_t.grad.cpu().numpy(), gg_ref, atol=1e-4, rtol=2e-5)
+
+
+@pytest.mark.parametrize("normalized", [True, False])
+def test_extension_entry_point_on_gathered_operands(W, normalized):
+    """_C.ctct_loss_simple_fwd (csrc/binding.cpp:103-222) through its C-ABI counterpart
+    ctct_b200_simple_gathered_forward: compose, lattice, occupancy gradient and the reductions in CUDA,
+    against the oracle's restatement of the same pieces."""
+    import warp_ctct._C as core
+    N, T, U1, V = 4, 45, 14, 30
+    f, g, ys, lx, ly = _case(N, T, U1, V, 41, (20, 45), (2, 13), repeat_prob=0.25)
+    cf, cg = oracle.collect_separate(f, g, ys)
+    den = oracle.log_matmul(f, g, np.float64).astype(np.float32) if normalized else None
+    g3 = oracle.compose_simple(cf, cg, den)
+    c64, gr64 = oracle.ctct_fwd(g3, ys, lx, ly, True, np.float64)
+    gcf, gcg, gden = oracle.simple_reduce(gr64.astype(np.float32), normalized)
+    cf_t, cg_t, ys_t, lx_t, ly_t = _dev(cf, cg, ys, lx, ly)
+    den_t = _dev(den)[0] if normalized else torch.empty(1, device=DEV)   # the reference passes a 1-D dummy for "none"
+    costs, grad_f, grad_g, grad_den = core.ctct_loss_simple_fwd(cf_t, cg_t, ys_t, den_t, lx_t, ly_t, True)
+    np.testing.assert_allclose(costs.cpu().numpy(), c64, rtol=1e-5)
+    assert grad_f.shape == cf_t.shape and grad_g.shape == cg_t.shape
+    np.testing.assert_allclose(grad_f.cpu().numpy(), gcf, atol=1e-4, rtol=2e-5)
+    np.testing.assert_allclose(grad_g.cpu().numpy(), gcg, atol=1e-4, rtol=2e-5)
+    if normalized:
+        np.testing.assert_allclose(grad_den.cpu().numpy(), gden, atol=1e-4, rtol=2e-5)
+    else:
+        assert grad_den is None
+    c2, a, b, c = core.ctct_loss_simple_fwd(cf_t, cg_t, ys_t, den_t, lx_t, ly_t, False)
+    assert a is None and b is None and c is None
+    np.testing.assert_allclose(c2.cpu().numpy(), c64, rtol=1e-5)
+    with pytest.raises(RuntimeError, match="length 3"):
+        core.ctct_loss_simple_fwd(cf_t, cg_t[..., :2].contiguous(), ys_t, den_t, lx_t, ly_t, True)
+    with pytest.raises(RuntimeError, match="matching the g at dim 1"):
+        core.ctct_loss_simple_fwd(cf_t[..., :5].contiguous(), cg_t, ys_t, den_t, lx_t, ly_t, True)
+
+
+def test_log_matmul_broadcasts_a_batch_of_one_on_the_right(W):
+    """csrc/logmatmul.cu:148-167 expands rhs to the batch of the result; forward and backward."""
+    from warp_ctct_b200.simple import log_matmul
+    rng = np.random.default_rng(12)
+    B, M, N, K = 3, 11, 7, 40
+    f = rng.standard_normal((B, M, K)).astype(np.float32)
+    g = rng.standard_normal((1, N, K)).astype(np.float32)
+    want = oracle.log_matmul(f, np.repeat(g, B, 0), np.float64)
+    f_t, g_t = _dev(f, g)
+    got = log_matmul(f_t, g_t.transpose(1, 2))
+    assert got.shape == (B, M, N)
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=0, atol=2e-5)
+    with pytest.raises(RuntimeError, match="expanded size"):
+        log_matmul(f_t[:1], _dev(np.repeat(g, B, 0))[0].transpose(1, 2))   # a batch of one on the LEFT does not broadcast
+    a, b = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    go = torch.from_numpy(rng.standard_normal((B, M, N)).astype(np.float32)).to(DEV)
+    W.LogMMExp.apply(a, b.transpose(1, 2), True, True).backward(go)
+    c, d = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    torch.logsumexp(c[:, :, None, :] + d[:, None, :, :], -1).backward(go)
+    assert b.grad.shape == d.grad.shape == (1, N, K)
+    assert (a.grad - c.grad).abs().max().item() < 2e-5 and (b.grad - d.grad).abs().max().item() < 5e-5

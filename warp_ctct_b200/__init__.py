@@ -330,6 +330,7 @@ def ctct_loss_and_grad(log_probs: T, labels: T, frames_lengths: T, labels_length
 
 
 from .logits import FusedLogitsCTCTLoss, FusedLogitsCTCTLossReduced, ctct_loss_from_logits  # noqa: E402,F401
+from .packed import FusedPackedCTCTLoss, ctct_loss_packed, pack_joint, unpack_joint  # noqa: E402,F401
 from .simple import (FusedSimpleCTCTLoss, LogMMExp, SimpleCTCTLoss, ctct_loss_simple_fwd,  # noqa: E402,F401
                      log_matmul, log_matmul_backward, log_matmul_tc)
 

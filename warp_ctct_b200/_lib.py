@@ -42,6 +42,15 @@ SIGNATURES = {
                                         _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "ctct_b200_logits_backward": (_int, [_vp, _vp, _int, _int, _int, C.c_float, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
                                          _i64, _int, _vp, _int, _vp]),
+    "ctct_b200_packed_offsets": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "ctct_b200_loss_forward_packed": (_int, [_vp, _int, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int, _int,
+                                             C.c_float, _vp, _vp, _vp, _vp, _sz, _vp, _sz, _vp]),
+    "ctct_b200_loss_backward_packed": (_int, [_vp, _vp, _int, _int, _int, C.c_float, _vp, _i64, _vp, _vp, _vp, _i64, _i64,
+                                              _i64, _i64, _int, _vp, _vp]),
+    "ctct_b200_logits_forward_packed": (_int, [_vp, _int, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int, _int,
+                                               C.c_float, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "ctct_b200_logits_backward_packed": (_int, [_vp, _vp, _int, _int, _int, C.c_float, _vp, _vp, _i64, _vp, _vp, _vp, _i64,
+                                                _i64, _i64, _i64, _int, _vp, _vp]),
     "ctct_b200_gather": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]),
     "ctct_b200_gather_probe": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp, _vp]),
     "ctct_b200_gathered_forward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
@@ -53,6 +62,9 @@ SIGNATURES = {
     "ctct_b200_log_matmul_backward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
     "ctct_b200_log_matmul_backward_tc": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),
     "ctct_b200_simple_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
+    "ctct_b200_simple_gathered_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
+    "ctct_b200_simple_gathered_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp,
+                                                 _vp, _sz, _vp]),
     "ctct_b200_simple_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
     "ctct_b200_simple_backward_tc": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp,
                                             _sz, _vp]),

@@ -235,7 +235,8 @@ bool is_pinned_host(const void *p) {
 
 template <typename InT>
 int launch_gather_t(const void *lp, const int *ys, const int *lx, const int *ly, float *out, int64_t N,
-                    int64_t T, int64_t U1, int64_t V, bool internal, int valid_only, cudaStream_t st, ClearSlice clear) {
+                    int64_t T, int64_t U1, int64_t V, bool internal, int valid_only, cudaStream_t st, ClearSlice clear,
+                    const int64_t *cu, int64_t packed_rows) {
     const int64_t total = internal ? N * T * U1 * 4 : N * T * U1 * 3;
     if (total == 0) return CTCT_OK;
     // a joint tensor in pinned host memory is read in place: no fill-size hint on those loads
@@ -251,25 +252,25 @@ int launch_gather_t(const void *lp, const int *ys, const int *lx, const int *ly,
     const bool small = total < (int64_t(1) << 31) - int64_t(own) * 256 * 4;
     if (internal) {
         if (small)
-            launch_pdl(k_gather3<InT, unsigned, true>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only, clear);
+            launch_pdl(k_gather3<InT, unsigned, true>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only, clear, cu, packed_rows);
         else
-            launch_pdl(k_gather3<InT, unsigned long long, true>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only, clear);
+            launch_pdl(k_gather3<InT, unsigned long long, true>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only, clear, cu, packed_rows);
     } else {
         if (small)
-            launch_pdl(k_gather3<InT, unsigned, false>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only, clear);
+            launch_pdl(k_gather3<InT, unsigned, false>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned)total, valid_only, clear, cu, packed_rows);
         else
-            launch_pdl(k_gather3<InT, unsigned long long, false>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only, clear);
+            launch_pdl(k_gather3<InT, unsigned long long, false>, dim3(grid), dim3(256), 0, st, p, ys, lx, ly, out, (int)T, (int)U1, (int)V, (unsigned long long)total, valid_only, clear, cu, packed_rows);
     }
     return check_launch("gather");
 }
 
 int launch_gather(const void *lp, int dtype, const int *ys, const int *lx, const int *ly, float *out, int64_t N,
                   int64_t T, int64_t U1, int64_t V, bool internal, int valid_only, cudaStream_t st,
-                  ClearSlice clear = kNoClear) {
+                  ClearSlice clear = kNoClear, const int64_t *cu = nullptr, int64_t packed_rows = 0) {
     switch (dtype) {
-    case CTCT_F32: return launch_gather_t<float>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st, clear);
-    case CTCT_F16: return launch_gather_t<__half>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st, clear);
-    case CTCT_BF16: return launch_gather_t<__nv_bfloat16>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st, clear);
+    case CTCT_F32: return launch_gather_t<float>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st, clear, cu, packed_rows);
+    case CTCT_F16: return launch_gather_t<__half>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st, clear, cu, packed_rows);
+    case CTCT_BF16: return launch_gather_t<__nv_bfloat16>(lp, ys, lx, ly, out, N, T, U1, V, internal, valid_only, st, clear, cu, packed_rows);
     }
     return CTCT_ERR_ARG;
 }
@@ -476,8 +477,10 @@ int launch_lse_gather_t(LseArgs a, cudaStream_t st) {
 }
 
 int launch_lse_gather(const void *logits, int dtype, const int *ys, const int *lx, const int *ly, float4 *G, int64_t N,
-                      int64_t T, int64_t U1, int64_t V, cudaStream_t st) {
+                      int64_t T, int64_t U1, int64_t V, cudaStream_t st, const int64_t *cu, int64_t packed_rows) {
     LseArgs a;
+    a.cu = cu;
+    a.packed_rows = packed_rows;
     a.logits = logits;
     a.ys = ys;
     a.lx = lx;
@@ -532,7 +535,7 @@ int dense_backward(DenseArgs a, int64_t N, int dtype, void *stream) {
 int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N,
                  int64_t T, int64_t U1, int64_t V, int want_grad, float *costs, float *grads3, void *workspace,
                  size_t workspace_bytes, void *stream, float *loss_out, ReduceSpec red, void *clear = nullptr,
-                 size_t clear_bytes = 0, bool from_logits = false) {
+                 size_t clear_bytes = 0, bool from_logits = false, const int64_t *cu = nullptr, int64_t packed_rows = 0) {
     if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
     if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
     if (N == 0) return CTCT_OK;
@@ -551,13 +554,14 @@ int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int3
     prof_mark(slot, 0, st);
     int rc;
     if (from_logits)  // log-softmax fused in: row log-sum-exp and the three picks in one streaming pass
-        rc = launch_lse_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float4 *>(ws + w.G), N, T, U1, V, st);
+        rc = launch_lse_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float4 *>(ws + w.G), N, T, U1, V, st, cu, packed_rows);
     else
-        rc = launch_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float *>(ws + w.G), N, T, U1, V, true, 1, st, cs[0]);
+        rc = launch_gather(log_probs, dtype, ys, lx, ly, reinterpret_cast<float *>(ws + w.G), N, T, U1, V, true, 1, st, cs[0], cu,
+                           packed_rows);
     if (rc) return rc;
     prof_mark(slot, 1, st);
     PadClear pad = kNoPad;
-    if (from_logits && clear && want_grad) {  // `clear` is the gradient buffer of the backward pass: zero its padding rows
+    if (from_logits && clear && want_grad && !cu) {  // `clear` is the gradient buffer of the backward pass: zero its padding rows
         const size_t esize = dtype == CTCT_F32 ? 4 : 2;
         if ((V * esize) % 16 || clear_bytes != static_cast<size_t>(N) * T * U1 * V * esize) return CTCT_ERR_ARG;
         pad.out = static_cast<unsigned char *>(clear);
@@ -594,7 +598,7 @@ int gather_probe_t(const float *lp, const int *ys, const int *lx, const int *ly,
     const int64_t cap = blocks_per_sm > 0 ? static_cast<int64_t>(sm_count()) * blocks_per_sm : want;
     const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
     launch_pdl(k_gather3<float, unsigned, true, PER>, dim3(grid), dim3(256), 0, st, lp, ys, lx, ly, out, (int)T, (int)U1, (int)V,
-               (unsigned)total, 1, kNoClear);
+               (unsigned)total, 1, kNoClear, static_cast<const int64_t *>(nullptr), int64_t(0));
     return check_launch("gather_probe");
 }
 
@@ -678,6 +682,8 @@ int ctct_b200_loss_backward_reduced(const float *grads3, const float *grad_loss,
     a.vec = 0;
     a.scalar_grad = 1;
     a.red = ReduceSpec{reduction, average_frames ? 1 : 0, norm};
+    a.cu = nullptr;
+    a.packed_rows = 0;
     return dense_backward(a, N, dtype, stream);
 }
 
@@ -701,6 +707,8 @@ int ctct_b200_loss_backward(const float *grads3, const float *grad_out, const in
     a.vec = 0;
     a.scalar_grad = 0;
     a.red = ReduceSpec{0, 0, 1.0f};
+    a.cu = nullptr;
+    a.packed_rows = 0;
     return dense_backward(a, N, dtype, stream);
 }
 
@@ -721,10 +729,10 @@ int ctct_b200_zero_fill(void *buffer, size_t bytes, void *stream) {
     return rc;
 }
 
-int ctct_b200_loss_backward_patch(const float *grads3, const float *grad, int scalar_grad, int reduction,
-                                  int average_frames, float norm, const int32_t *ys, const int32_t *lx,
-                                  const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int dtype,
-                                  void *dense, void *stream) {
+static int backward_patch_impl(const float *grads3, const float *grad, int scalar_grad, int reduction, int average_frames,
+                               float norm, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N, int64_t T,
+                               int64_t U1, int64_t V, int dtype, void *dense, void *stream, const int64_t *cu,
+                               int64_t packed_rows = 0) {
     if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
     if (scalar_grad && ((reduction != 1 && reduction != 2) || !(norm > 0.0f))) return CTCT_ERR_ARG;
     if (N == 0 || T == 0) return CTCT_OK;
@@ -743,7 +751,47 @@ int ctct_b200_loss_backward_patch(const float *grads3, const float *grad, int sc
     a.vec = 2;
     a.scalar_grad = scalar_grad ? 1 : 0;
     a.red = ReduceSpec{scalar_grad ? reduction : 0, average_frames ? 1 : 0, scalar_grad ? norm : 1.0f};
+    a.cu = cu;
+    a.packed_rows = packed_rows;
     return dense_backward(a, N, dtype, stream);
+}
+
+int ctct_b200_loss_backward_patch(const float *grads3, const float *grad, int scalar_grad, int reduction,
+                                  int average_frames, float norm, const int32_t *ys, const int32_t *lx,
+                                  const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V, int dtype,
+                                  void *dense, void *stream) {
+    return backward_patch_impl(grads3, grad, scalar_grad, reduction, average_frames, norm, ys, lx, ly, N, T, U1, V, dtype, dense,
+                               stream, nullptr);
+}
+
+// ---- packed (ragged) layout: only the valid rows of every utterance exist -----------------------
+int ctct_b200_packed_offsets(const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t *cu_rows,
+                             void *stream) {
+    if (N < 0 || N > 65535 || T < 0 || U1 < 1 || !cu_rows || (N > 0 && (!lx || !ly))) return CTCT_ERR_ARG;
+    k_packed_offsets<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(lx, ly, (int)N, (int)T, (int)U1, cu_rows);
+    return check_launch("packed_offsets");
+}
+
+int ctct_b200_loss_forward_packed(const void *packed, int dtype, const int64_t *cu_rows, int64_t packed_rows, const int32_t *ys,
+                                  const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
+                                  int want_grad, int reduction, int average_frames, float norm, float *costs, float *loss,
+                                  float *grads3, void *clear, size_t clear_bytes, void *workspace, size_t workspace_bytes,
+                                  void *stream) {
+    if (reduction < 0 || reduction > 2 || !cu_rows || packed_rows < 0) return CTCT_ERR_ARG;
+    if (reduction != 0 && (!loss || !(norm > 0.0f))) return CTCT_ERR_ARG;
+    if (packed && is_pinned_host(packed)) return CTCT_ERR_ARG;
+    return forward_impl(packed, dtype, ys, lx, ly, N, T, U1, V, want_grad, costs, grads3, workspace, workspace_bytes, stream,
+                        reduction ? loss : nullptr, ReduceSpec{reduction, average_frames ? 1 : 0, reduction ? norm : 1.0f},
+                        clear, clear_bytes, false, cu_rows, packed_rows);
+}
+
+int ctct_b200_loss_backward_packed(const float *grads3, const float *grad, int scalar_grad, int reduction,
+                                   int average_frames, float norm, const int64_t *cu_rows, int64_t packed_rows,
+                                   const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N, int64_t T,
+                                   int64_t U1, int64_t V, int dtype, void *packed_grad, void *stream) {
+    if (!cu_rows || packed_rows < 0) return CTCT_ERR_ARG;
+    return backward_patch_impl(grads3, grad, scalar_grad, reduction, average_frames, norm, ys, lx, ly, N, T, U1, V, dtype,
+                               packed_grad, stream, cu_rows, packed_rows);
 }
 
 int ctct_b200_logits_forward(const void *logits, int dtype, const int32_t *ys, const int32_t *lx, const int32_t *ly,
@@ -760,10 +808,24 @@ int ctct_b200_logits_forward(const void *logits, int dtype, const int32_t *ys, c
                         grad_logits, grad_logits ? static_cast<size_t>(N) * T * U1 * V * esize : 0, true);
 }
 
-int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar_grad, int reduction, int average_frames,
-                              float norm, const void *logits, const int32_t *ys, const int32_t *lx, const int32_t *ly,
-                              int64_t N, int64_t T, int64_t U1, int64_t V, int dtype, void *grad_logits,
-                              int padding_cleared, void *stream) {
+int ctct_b200_logits_forward_packed(const void *packed_logits, int dtype, const int64_t *cu_rows, int64_t packed_rows,
+                                    const int32_t *ys,
+                                    const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1, int64_t V,
+                                    int want_grad, int reduction, int average_frames, float norm, float *costs, float *loss,
+                                    float *grads3, void *workspace, size_t workspace_bytes, void *stream) {
+    if (reduction < 0 || reduction > 2 || !cu_rows || packed_rows < 0) return CTCT_ERR_ARG;
+    if (reduction != 0 && (!loss || !(norm > 0.0f))) return CTCT_ERR_ARG;
+    if (packed_logits && is_pinned_host(packed_logits)) return CTCT_ERR_ARG;
+    return forward_impl(packed_logits, dtype, ys, lx, ly, N, T, U1, V, want_grad, costs, grads3, workspace, workspace_bytes,
+                        stream, reduction ? loss : nullptr,
+                        ReduceSpec{reduction, average_frames ? 1 : 0, reduction ? norm : 1.0f}, nullptr, 0, true, cu_rows,
+                        packed_rows);
+}
+
+static int logits_backward_impl(const float *grads3, const float *grad, int scalar_grad, int reduction, int average_frames,
+                                float norm, const void *logits, const int32_t *ys, const int32_t *lx, const int32_t *ly,
+                                int64_t N, int64_t T, int64_t U1, int64_t V, int dtype, void *grad_logits,
+                                int padding_cleared, void *stream, const int64_t *cu, int64_t packed_rows = 0) {
     if (!dims_ok(N, T, U1) || V < 1 || V > 0x7fffffff) return CTCT_ERR_ARG;
     if (dtype != CTCT_F32 && dtype != CTCT_F16 && dtype != CTCT_BF16) return CTCT_ERR_ARG;
     if (scalar_grad && ((reduction != 1 && reduction != 2) || !(norm > 0.0f))) return CTCT_ERR_ARG;
@@ -787,6 +849,8 @@ int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar
     a.red = ReduceSpec{scalar_grad ? reduction : 0, average_frames ? 1 : 0, scalar_grad ? norm : 1.0f};
     a.rows = N * T * U1;
     a.padding_cleared = padding_cleared ? 1 : 0;
+    a.cu = cu;
+    a.packed_rows = packed_rows;
     cudaEvent_t *slot = prof_slot(7);
     prof_mark(slot, 0, st);
     int rc = CTCT_ERR_ARG;
@@ -797,6 +861,23 @@ int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar
     }
     prof_mark(slot, 1, st);
     return rc;
+}
+
+int ctct_b200_logits_backward(const float *grads3, const float *grad, int scalar_grad, int reduction, int average_frames,
+                              float norm, const void *logits, const int32_t *ys, const int32_t *lx, const int32_t *ly,
+                              int64_t N, int64_t T, int64_t U1, int64_t V, int dtype, void *grad_logits,
+                              int padding_cleared, void *stream) {
+    return logits_backward_impl(grads3, grad, scalar_grad, reduction, average_frames, norm, logits, ys, lx, ly, N, T, U1, V,
+                                dtype, grad_logits, padding_cleared, stream, nullptr);
+}
+
+int ctct_b200_logits_backward_packed(const float *grads3, const float *grad, int scalar_grad, int reduction,
+                                     int average_frames, float norm, const void *packed_logits, const int64_t *cu_rows,
+                                     int64_t packed_rows, const int32_t *ys, const int32_t *lx, const int32_t *ly, int64_t N, int64_t T,
+                                     int64_t U1, int64_t V, int dtype, void *packed_grad, void *stream) {
+    if (!cu_rows || packed_rows < 0) return CTCT_ERR_ARG;
+    return logits_backward_impl(grads3, grad, scalar_grad, reduction, average_frames, norm, packed_logits, ys, lx, ly, N, T, U1,
+                                V, dtype, packed_grad, 0, stream, cu_rows, packed_rows);
 }
 
 int ctct_b200_gather(const void *log_probs, int dtype, const int32_t *ys, const int32_t *lx, const int32_t *ly,
@@ -1011,6 +1092,65 @@ int ctct_b200_simple_forward(const float *f, const float *g, const float *den, c
     if (want_grad) rc = launch_fill_grad(w, ws, ys, lx, ly, grads3, 0, N, T, U1, st);
     prof_mark(slot, 3, st);
     return rc;
+}
+
+size_t ctct_b200_simple_gathered_workspace_bytes(int64_t N, int64_t T, int64_t U1, int want_grad) {
+    WsLayout w;
+    if (!dims_ok(N, T, U1) || !ws_layout(N, T, U1, want_grad, &w)) return 0;
+    return w.total + (want_grad ? align256(static_cast<size_t>(N) * T * U1 * sizeof(float4)) : 0);
+}
+
+int ctct_b200_simple_gathered_forward(const float *f, const float *g, const float *den, const int32_t *ys,
+                                      const int32_t *lx, const int32_t *ly, int64_t N, int64_t T, int64_t U1,
+                                      int want_grad, float *costs, float *grad_f, float *grad_g, float *grad_den,
+                                      void *workspace, size_t workspace_bytes, void *stream) {
+    if (!dims_ok(N, T, U1)) return CTCT_ERR_ARG;
+    if (N == 0) return CTCT_OK;
+    if (!f || !g || !lx || !ly || !costs || (U1 > 1 && !ys)) return CTCT_ERR_ARG;
+    if (want_grad && (!grad_f || !grad_g || (den && !grad_den))) return CTCT_ERR_ARG;
+    WsLayout w;
+    if (!ws_layout(N, T, U1, want_grad, &w)) return CTCT_ERR_UNSUPPORTED;
+    const size_t need = w.total + (want_grad ? align256(static_cast<size_t>(N) * T * U1 * sizeof(float4)) : 0);
+    if (!workspace || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256) return CTCT_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char *ws = static_cast<char *>(workspace);
+    float *grads3 = reinterpret_cast<float *>(ws + w.total);
+    GatheredArgs c;
+    c.f = f;
+    c.g = g;
+    c.den = den;
+    c.lx = lx;
+    c.ly = ly;
+    c.G = reinterpret_cast<float4 *>(ws + w.G);
+    c.T = (int)T;
+    c.U1 = (int)U1;
+    c.rows = N * T * U1;
+    if (c.rows > 0) {
+        const int64_t want = (c.rows + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+        launch_pdl(k_gathered_compose, dim3(static_cast<unsigned>(want < cap ? want : cap)), dim3(256), 0, st, c);
+        int rc = check_launch("gathered_compose");
+        if (rc) return rc;
+    }
+    int rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st);
+    if (rc || !want_grad) return rc;
+    rc = launch_fill_grad(w, ws, ys, lx, ly, grads3, 0, N, T, U1, st);
+    if (rc || T == 0) return rc;
+    GatheredReduceArgs r;
+    r.grads3 = reinterpret_cast<const float4 *>(grads3);
+    r.lx = lx;
+    r.ly = ly;
+    r.grad_f = grad_f;
+    r.grad_g = grad_g;
+    r.grad_den = den ? grad_den : nullptr;
+    r.N = (int)N;
+    r.T = (int)T;
+    r.U1 = (int)U1;
+    launch_pdl(k_gathered_reduce_t, dim3(static_cast<unsigned>((N * T + 7) / 8)), dim3(256), 0, st, r);
+    rc = check_launch("gathered_reduce_t");
+    if (rc) return rc;
+    launch_pdl(k_gathered_reduce_u, dim3(static_cast<unsigned>((N * U1 + 7) / 8)), dim3(256), 0, st, r);
+    return check_launch("gathered_reduce_u");
 }
 
 // tensor-core gradient through the denominator; planes, maxima and flags are those the forward

@@ -12,6 +12,8 @@
 
 namespace ctct {
 
+// `cu` != nullptr: the joint tensor is PACKED, (total rows, V) with only the valid rows of every
+// utterance (needs valid_only); the output keeps the padded [N][T][U1] record layout either way.
 // INTERNAL = true : out[n][t][u] = one 16-byte record {blank, repeat-label, next-label, 0}, values
 //                   converted to log2 units and clamped at NEG; everything outside t < lx,
 //                   u <= ly is written as 0
@@ -20,7 +22,8 @@ template <typename InT, typename IdxT, bool INTERNAL, int PER = 4>
 __global__ void __launch_bounds__(256)
 k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__restrict__ lx,
           const int *__restrict__ ly, float *__restrict__ out, int T, int U1, int V,
-          IdxT total, int mode, const ClearSlice clear) {
+          IdxT total, int mode, const ClearSlice clear, const int64_t *__restrict__ cu = nullptr,
+          int64_t packed_rows = 0) {
     // everything before this launch is done before anything here runs; from then on the next launch
     // (the lattice with its clearing blocks) may move in beside this one
     pdl_wait();
@@ -62,8 +65,11 @@ k_gather3(const InT *__restrict__ lp, const int *__restrict__ ys, const int *__r
                     // with valid_only the label ys[n,u] is a real one only for u < ly[n]
                     if (k == 2 && u < U && (!valid_only || u < ly[n])) idx = ys[static_cast<int64_t>(n) * U + u];
                     idx = min(max(idx, 0), V - 1);
-                    const int64_t row = static_cast<int64_t>(nt) * U1 + u;
-                    const float x = remote ? load_remote(lp + row * V + idx) : load_sparse(lp + row * V + idx);
+                    // packed input: utterance n owns rows [cu[n], cu[n+1]), frame-major, ly[n]+1 rows per frame
+                    const int64_t row = cu ? cu[n] + static_cast<int64_t>(t) * (ly[n] + 1) + u : static_cast<int64_t>(nt) * U1 + u;
+                    float x = 0.0f;
+                    // lengths that do not agree with the packed tensor must not read past its end
+                    if (cu == nullptr || row < packed_rows) x = remote ? load_remote(lp + row * V + idx) : load_sparse(lp + row * V + idx);
                     val[j] = INTERNAL ? to_log2(x) : x;
                 }
             }

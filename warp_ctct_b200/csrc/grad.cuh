@@ -214,7 +214,37 @@ struct DenseArgs {
     // scale is grad_out[0] * utterance_weight(red, lx[n]); otherwise grad_out holds N floats
     int scalar_grad;
     ReduceSpec red;
+    const int64_t *cu;      // packed output: row offsets per utterance (N+1), nullptr = padded (N,T,U1,V)
+    int64_t packed_rows;    // rows of the packed output (rows beyond it are never written)
 };
+
+// Row offsets of the packed layout: cu[n] = sum_{m<n} lx[m] * (ly[m] + 1), cu[N] = total rows.
+// One block; N <= 65535.
+__global__ void __launch_bounds__(1024) k_packed_offsets(const int *__restrict__ lx, const int *__restrict__ ly, int N, int T,
+                                                         int U1, int64_t *__restrict__ cu) {
+    __shared__ long long part[1024];
+    const int per = (N + 1023) / 1024;
+    const int lo = threadIdx.x * per, hi = min(N, lo + per);
+    long long s = 0;
+    for (int n = lo; n < hi; ++n) s += static_cast<long long>(max(0, min(lx[n], T))) * (max(0, min(ly[n], U1 - 1)) + 1);
+    part[threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        long long run = 0;
+        for (int i = 0; i < 1024; ++i) {
+            const long long v = part[i];
+            part[i] = run;
+            run += v;
+        }
+        cu[N] = run;
+    }
+    __syncthreads();
+    long long run = part[threadIdx.x];
+    for (int n = lo; n < hi; ++n) {
+        cu[n] = run;
+        run += static_cast<long long>(max(0, min(lx[n], T))) * (max(0, min(ly[n], U1 - 1)) + 1);
+    }
+}
 
 // What one row of the dense gradient holds besides zeros: column 0 and up to two label columns.
 template <typename OutT>
@@ -422,7 +452,9 @@ __global__ void __launch_bounds__(256) k_dense_patch(const DenseArgs a, int64_t 
         const int y_prev = (u >= 1) ? y[u - 1] : 0;
         const int y_next = (u < Un) ? y[u] : 0;
         const RowPatch<OutT> p = make_patch<OutT>(a.GR[r], go, y_prev, y_next, u, Un, V);
-        OutT *row = static_cast<OutT *>(a.out) + r * V;
+        const int64_t r_out = a.cu ? a.cu[n] + static_cast<int64_t>(t) * (Un + 1) + u : r;
+        if (a.cu && r_out >= a.packed_rows) continue;
+        OutT *row = static_cast<OutT *>(a.out) + r_out * V;
         if (SECTORS) {
             const int s1 = p.i1 >= 0 ? p.i1 / ES : 0, s2 = p.i2 >= 0 ? p.i2 / ES : 0;
             write_sector<OutT>(row, 0, p);

@@ -111,6 +111,8 @@ struct LseArgs {
     int T, U1, V;
     int64_t rows;        // N*T*U1
     int vec;             // V is a multiple of the 16-byte vector width and the base is 16-byte aligned
+    const int64_t *cu;   // packed logits (total valid rows, V): row offsets per utterance; nullptr = padded
+    int64_t packed_rows; // rows of the packed tensor (slabs reaching beyond it are treated as padding)
 };
 
 // One CTA per (n,t) slab of U1 rows (a contiguous U1*V block of the tensor), one warp per row, rows
@@ -138,11 +140,13 @@ __global__ void __launch_bounds__(256, LOGITS_BLOCKS_PER_SM) k_lse_gather(const 
     const int n = static_cast<int>(nt / a.T);
     const int t = static_cast<int>(nt - static_cast<int64_t>(n) * a.T);
     const int U1 = a.U1, U = U1 - 1;
-    const int Un = (t < a.lx[n]) ? min(a.ly[n], U) : -1;  // rows u <= Un are read
+    int Un = (t < a.lx[n]) ? min(a.ly[n], U) : -1;  // rows u <= Un are read
+    if (a.cu && Un >= 0 && a.cu[n] + static_cast<int64_t>(t + 1) * (Un + 1) > a.packed_rows) Un = -1;
     float4 *Gs = a.G + nt * U1;
     // records of the padding rows
     for (int u = Un + 1 + static_cast<int>(threadIdx.x); u < U1; u += 256) Gs[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    const InT *slab = static_cast<const InT *>(a.logits) + nt * U1 * a.V;
+    const int64_t slab_row = a.cu ? a.cu[n] + static_cast<int64_t>(t) * (Un + 1) : nt * U1;
+    const InT *slab = static_cast<const InT *>(a.logits) + slab_row * a.V;
     const int *y = a.ys + static_cast<int64_t>(n) * U;
     const float NINF = -__int_as_float(0x7f800000);
 
@@ -286,6 +290,8 @@ struct LogitsGradArgs {
     ReduceSpec red;
     int64_t rows;
     int padding_cleared;    // the padding rows of `out` are zero already (cleared during the forward pass)
+    const int64_t *cu;      // packed logits and gradient: row offsets per utterance; nullptr = padded
+    int64_t packed_rows;
 };
 
 // One CTA per (n,t) slab again, one warp per row.  Padding rows are streamed out as zeros; a valid
@@ -301,9 +307,11 @@ __global__ void __launch_bounds__(256, LOGITS_BLOCKS_PER_SM) k_logits_grad(const
     const int t = static_cast<int>(nt - static_cast<int64_t>(n) * a.T);
     const int U1 = a.U1, U = U1 - 1, V = a.V;
     const int lx_n = a.lx[n];
-    const int Un = (t < lx_n) ? min(a.ly[n], U) : -1;
-    const T *slab_in = static_cast<const T *>(a.logits) + nt * U1 * V;
-    T *slab_out = static_cast<T *>(a.out) + nt * U1 * V;
+    int Un = (t < lx_n) ? min(a.ly[n], U) : -1;
+    if (a.cu && Un >= 0 && a.cu[n] + static_cast<int64_t>(t + 1) * (Un + 1) > a.packed_rows) Un = -1;
+    const int64_t slab_row = a.cu ? a.cu[n] + static_cast<int64_t>(t) * (Un + 1) : nt * U1;
+    const T *slab_in = static_cast<const T *>(a.logits) + slab_row * V;
+    T *slab_out = static_cast<T *>(a.out) + slab_row * V;
     const uint4 z = make_uint4(0u, 0u, 0u, 0u);
     const int *y = a.ys + static_cast<int64_t>(n) * U;
     const float4 *grs = a.GR + nt * U1;
@@ -311,7 +319,7 @@ __global__ void __launch_bounds__(256, LOGITS_BLOCKS_PER_SM) k_logits_grad(const
     if (Un >= 0) go = a.scalar_grad ? a.grad_out[0] * utterance_weight(a.red, lx_n) : a.grad_out[n];
 
     // padding rows of the slab form one contiguous block: all 256 threads stream zeros over it
-    if (!a.padding_cleared) {
+    if (!a.padding_cleared && a.cu == nullptr) {  // a packed tensor has no padding rows
         T *pad = slab_out + static_cast<int64_t>(Un + 1) * V;
         const int64_t count = static_cast<int64_t>(U1 - (Un + 1)) * V;
         if (a.vec) {

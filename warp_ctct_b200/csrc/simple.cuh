@@ -274,4 +274,106 @@ __global__ void __launch_bounds__(256) k_simple_patch_g(const PatchArgs a, int N
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Pre-gathered form, the reference's extension entry point ctct_loss_simple_fwd (csrc/binding.cpp:103-222):
+// f (N,T,U1) already holds f[n,t,{0, ys[0], ..., ys[U-1]}], g (N,U1,3) the three picks per context.
+
+struct GatheredArgs {
+    const float *f;    // (N,T,U1)
+    const float *g;    // (N,U1,3)
+    const float *den;  // (N,T,U1) or nullptr
+    const int *lx, *ly;
+    float4 *G;         // [N][T][U1] records out (log2 units), 0 outside the valid region
+    int T, U1;
+    int64_t rows;      // N*T*U1
+};
+
+// log-prob of slot k at (n,t,u), csrc/simple.cu:20-26 (LOGPROBB, LOGPROBY): blank f[n,t,0] + g[n,u,0];
+// repeat f[n,t,u] + g[n,u,1]; next f[n,t,u+1] + g[n,u,2]; each minus den[n,t,u] when normalised.
+__global__ void __launch_bounds__(256) k_gathered_compose(const GatheredArgs a) {
+    pdl_wait();
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < a.rows;
+         r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t nt = r / a.U1;
+        const int u = static_cast<int>(r - nt * a.U1);
+        const int n = static_cast<int>(nt / a.T);
+        const int t = static_cast<int>(nt - static_cast<int64_t>(n) * a.T);
+        float4 rec = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (t < a.lx[n] && u <= a.ly[n]) {
+            const float *fr = a.f + nt * a.U1;
+            const float *gr = a.g + (static_cast<int64_t>(n) * a.U1 + u) * 3;
+            const float d = a.den ? a.den[r] : 0.0f;
+            float x0 = fr[0] + gr[0], x1 = fr[u] + gr[1], x2 = (u + 1 < a.U1) ? fr[u + 1] + gr[2] : 0.0f;
+            if (a.den) {
+                x0 -= d;
+                x1 -= d;
+                x2 -= d;
+            }
+            rec = make_float4(to_log2(x0), to_log2(x1), to_log2(x2), 0.0f);
+        }
+        a.G[r] = rec;
+    }
+}
+
+struct GatheredReduceArgs {
+    const float4 *grads3;  // [N][T][U1] {g0,g1,g2,0}
+    const int *lx, *ly;
+    float *grad_f;         // (N,T,U1)
+    float *grad_g;         // (N,U1,3)
+    float *grad_den;       // (N,T,U1) or nullptr
+    int N, T, U1;
+};
+
+// The reductions of csrc/binding.cpp:198,209-219 for one frame per warp: grad_den = -(g0+g1+g2);
+// grad_f[...,0] = sum_u g0; grad_f[...,k] = g1[k] + g2[k-1].  Fixed summation order.
+__global__ void __launch_bounds__(256) k_gathered_reduce_t(const GatheredReduceArgs a) {
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t nt = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (nt >= static_cast<int64_t>(a.N) * a.T) return;
+    const float4 *g3 = a.grads3 + nt * a.U1;
+    float *gf = a.grad_f + nt * a.U1;
+    float blank = 0.0f;
+    for (int u = lane; u < a.U1; u += 32) {
+        const float4 cur = g3[u];
+        blank += cur.x;
+        if (a.grad_den) a.grad_den[nt * a.U1 + u] = -(cur.x + cur.y + cur.z);
+        if (u >= 1) gf[u] = cur.y + g3[u - 1].z;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) blank += __shfl_xor_sync(0xffffffffu, blank, o);
+    if (lane == 0) gf[0] = blank;
+}
+
+// grad_g[n,u,k] = sum_t grads[n,t,u,k]: one warp per (n,u), fixed summation order.
+__global__ void __launch_bounds__(256) k_gathered_reduce_u(const GatheredReduceArgs a) {
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (w >= static_cast<int64_t>(a.N) * a.U1) return;
+    const int n = static_cast<int>(w / a.U1), u = static_cast<int>(w - static_cast<int64_t>(n) * a.U1);
+    const int Tn = max(0, min(a.lx[n], a.T));
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f;
+    if (u <= a.ly[n]) {
+        for (int t = lane; t < Tn; t += 32) {
+            const float4 g3 = a.grads3[(static_cast<int64_t>(n) * a.T + t) * a.U1 + u];
+            s0 += g3.x;
+            s1 += g3.y;
+            s2 += g3.z;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if (lane == 0) {
+        float *o = a.grad_g + w * 3;
+        o[0] = s0;
+        o[1] = s1;
+        o[2] = s2;
+    }
+}
+
 }  // namespace ctct

@@ -34,15 +34,21 @@ def log_matmul(lhs: T, rhs: T) -> T:
         raise RuntimeError("need cuda tensors")
     if lhs.device != rhs.device:
         raise RuntimeError("need tensors on same GPU")
-    if lhs.dim() != 3 or rhs.dim() != 3 or lhs.size(2) != rhs.size(1) or lhs.size(0) != rhs.size(0):
+    if lhs.dim() != 3 or rhs.dim() != 3 or lhs.size(2) != rhs.size(1):
         raise RuntimeError("invalid sizes")
     B, M, K = lhs.shape
     N = rhs.size(2)
+    # the result has the batch of lhs; rhs is expanded to it (csrc/logmatmul.cu:148-167), so a
+    # batch of one on the right broadcasts (batch stride 0) and anything else must match
+    if rhs.size(0) != B and rhs.size(0) != 1:
+        raise RuntimeError(f"The expanded size of the tensor ({B}) must match the existing size ({rhs.size(0)}) at "
+                           f"non-singleton dimension 0")
+    rhs_sb = rhs.stride(0) if rhs.size(0) == B else 0
     out = torch.empty((B, M, N), dtype=torch.float32, device=lhs.device)
     with torch.cuda.device(lhs.device):
         rc = _lib.lib().ctct_b200_log_matmul(
             _lib.ptr(lhs), lhs.stride(0), lhs.stride(1), lhs.stride(2),
-            _lib.ptr(rhs), rhs.stride(0), rhs.stride(1), rhs.stride(2),
+            _lib.ptr(rhs), rhs_sb, rhs.stride(1), rhs.stride(2),
             B, M, K, N, _lib.ptr(out), _lib.stream_ptr(lhs.device))
     _lib.check(rc, "ctct_b200_log_matmul")
     return out
@@ -81,6 +87,9 @@ def log_matmul_backward(grad_out: Optional[T], lhs: T, rhs: T, res: T, grad_mask
     N = rhs.size(2)
     dev = lhs.device
     lhs_c = lhs.contiguous()
+    broadcast_rhs = rhs.size(0) == 1 and B > 1   # undone below by a sum over the batch (csrc/binding.cpp:285-292)
+    if broadcast_rhs:
+        rhs = rhs.expand(B, -1, -1)
     rhs_t = rhs.transpose(1, 2).contiguous()  # (B,N,K); free when rhs is a transposed view
     go = grad_out.to(torch.float32).contiguous()
     res_c = res.contiguous()
@@ -91,6 +100,8 @@ def log_matmul_backward(grad_out: Optional[T], lhs: T, rhs: T, res: T, grad_mask
             _lib.ptr(go), _lib.ptr(lhs_c), _lib.ptr(rhs_t), _lib.ptr(res_c), B, M, K, N,
             _lib.ptr(grad_lhs), _lib.ptr(grad_rhs_t), _lib.stream_ptr(dev))
     _lib.check(rc, "ctct_b200_log_matmul_backward")
+    if grad_rhs_t is not None and broadcast_rhs:
+        grad_rhs_t = grad_rhs_t.sum(0, keepdim=True)
     return grad_lhs, (grad_rhs_t.transpose(1, 2) if grad_rhs_t is not None else None)
 
 
@@ -248,24 +259,25 @@ def ctct_loss_simple_fwd(f: T, g: T, ys: T, den: T, lx: T, ly: T, requires_grad:
         _require_cuda(den=den)
         if den.dtype != torch.float32:
             raise RuntimeError("den must be a Float tensor")
-    # log-prob of slot k at (n,t,u): csrc/simple.cu:20-26
+    # compose f + g - den (csrc/simple.cu:20-26), lattice, occupancy gradient and the reductions of
+    # csrc/binding.cpp:198,209-219: one C-ABI call, all CUDA
     N, Tm, U1 = f.shape
-    fb = f[:, :, :1].unsqueeze(-1)                       # blank column of f
-    f1 = f.unsqueeze(-1)                                 # f[n,t,u]   (label u-1 at context u)
-    f2 = torch.cat([f[:, :, 1:], f[:, :, :1]], dim=2).unsqueeze(-1)  # f[n,t,u+1]; last context never uses it
-    lp = torch.cat([fb.expand(-1, -1, U1, -1), f1, f2], dim=-1) + g.unsqueeze(1)
-    if normalized:
-        lp = lp - den.unsqueeze(-1)
-    from . import ctct_loss_fwd
-    costs, grads = ctct_loss_fwd(lp.contiguous(), ys, lx, ly, requires_grad)
-    if not requires_grad:
-        return costs, None, None, None
-    # reductions of csrc/binding.cpp:198,209-219
-    grad_den = -grads.sum(3) if normalized else None
-    grad_g = grads.sum(1)
-    grad_f = torch.empty_like(f)
-    grad_f[..., 0] = grads[..., 0].sum(2)
-    grad_f[..., 1:] = grads[..., 1:, 1] + grads[..., :U1 - 1, 2]
+    dev = f.device
+    lib = _lib.lib()
+    costs = torch.empty((N,), dtype=torch.float32, device=dev)
+    grad_f = torch.empty_like(f) if requires_grad else None
+    grad_g = torch.empty_like(g) if requires_grad else None
+    grad_den = torch.empty_like(den) if (requires_grad and normalized) else None
+    with torch.cuda.device(dev):
+        nbytes = lib.ctct_b200_simple_gathered_workspace_bytes(N, Tm, U1, int(requires_grad))
+        if nbytes == 0 and N > 0:
+            raise RuntimeError(f"unsupported problem size N={N}, T={Tm}, U+1={U1}")
+        ws = torch.empty((max(nbytes, 256),), dtype=torch.uint8, device=dev)
+        rc = lib.ctct_b200_simple_gathered_forward(
+            _lib.ptr(f), _lib.ptr(g), _lib.ptr(den) if normalized else None, _lib.ptr(ys), _lib.ptr(lx), _lib.ptr(ly),
+            N, Tm, U1, int(requires_grad), _lib.ptr(costs), _lib.ptr(grad_f), _lib.ptr(grad_g), _lib.ptr(grad_den),
+            _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+    _lib.check(rc, "ctct_b200_simple_gathered_forward")
     return costs, grad_f, grad_g, grad_den
 
 
