@@ -428,9 +428,11 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
 
     def loss_of(x, y, a, b):
         if packed:
-            from warp_ctct_b200.sharded import all_reduce_sum
-            return all_reduce_sum(W.ctct_loss_packed(x, y, a, b, reduction="mean", max_frames=T, from_logits=logits,
-                                                     global_batch=G))
+            loss_p = W.ctct_loss_packed(x, y, a, b, reduction="mean", max_frames=T, from_logits=logits, global_batch=G)
+            if world > 1:
+                from warp_ctct_b200.sharded import all_reduce_sum
+                loss_p = all_reduce_sum(loss_p)
+            return loss_p
         return sharded_ctct_loss(x, y, a, b, global_batch=G, reduction="mean", from_logits=logits)
 
     def step():

@@ -25,7 +25,7 @@ def _forward(ctx, logits: T, labels: T, lx: T, ly: T, requires_grad: bool, red: 
     dev = logits.device
     lib = _lib.lib()
     g3_bytes, ws_bytes = _sizes(N, Tm, U1, requires_grad)
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         out = torch.empty((N + 1,), dtype=torch.float32, device=dev)
         buf = torch.empty((g3_bytes + ws_bytes,), dtype=torch.uint8, device=dev)  # [compact gradient | workspace]
         # The gradient buffer is allocated now so that the lattice launch can zero its padding rows
@@ -38,7 +38,7 @@ def _forward(ctx, logits: T, labels: T, lx: T, ly: T, requires_grad: bool, red: 
         rc = lib.ctct_b200_logits_forward(
             logits.data_ptr(), _lib.dtype_code(logits.dtype), labels.data_ptr(), lx.data_ptr(), ly.data_ptr(),
             N, Tm, U1, V, int(requires_grad), red, int(average_frames), norm, out.data_ptr() + 4, out.data_ptr(),
-            base if requires_grad else None, _lib.ptr(grad), base + g3_bytes, ws_bytes, _lib.stream_ptr(dev))
+            base if requires_grad else None, _lib.ptr(grad), base + g3_bytes, ws_bytes, _lib.raw_stream(dev))
     _lib.check(rc, "ctct_b200_logits_forward")
     if requires_grad:
         ctx.save_for_backward(buf, logits, labels, lx, ly)
@@ -54,13 +54,13 @@ def _backward(ctx, grad: T) -> T:
     go = grad.to(torch.float32).contiguous()
     out, ctx.cleared = ctx.cleared, None   # a second backward through a retained graph gets a fresh buffer
     cleared = out is not None
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         if out is None:
             out = torch.empty_like(logits)
         rc = _lib.lib().ctct_b200_logits_backward(
             buf.data_ptr(), go.data_ptr(), int(red != 0), red, int(avg), norm, logits.data_ptr(), labels.data_ptr(),
             lx.data_ptr(), ly.data_ptr(), N, Tm, U1, V, _lib.dtype_code(logits.dtype), out.data_ptr(), int(cleared),
-            _lib.stream_ptr(dev))
+            _lib.raw_stream(dev))
     _lib.check(rc, "ctct_b200_logits_backward")
     return out
 

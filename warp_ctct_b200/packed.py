@@ -39,7 +39,8 @@ def unpack_joint(packed: T, frames_lengths: T, labels_lengths: T, max_frames: in
 
 
 class FusedPackedCTCTLoss(torch.autograd.Function):
-    """[loss, costs...] from a packed joint tensor; gradient of the same packed shape."""
+    """The reduced loss (red = 1 'sum', 2 'mean') or the per-utterance costs (red = 0) from a packed
+    joint tensor; gradient of the same packed shape."""
 
     @staticmethod
     def forward(ctx, packed: T, labels: T, lx: T, ly: T, requires_grad: bool, red: int, average_frames: bool, norm: float,
@@ -51,8 +52,8 @@ class FusedPackedCTCTLoss(torch.autograd.Function):
         lib = _lib.lib()
         g3_bytes, ws_bytes = _sizes(N, max_frames, U1, requires_grad)
         esize = packed.element_size()
-        with torch.cuda.device(dev):
-            st = _lib.stream_ptr(dev)
+        with _lib.on_device(dev):
+            st = _lib.raw_stream(dev)
             out = torch.empty((N + 1,), dtype=torch.float32, device=dev)
             cu = torch.empty((N + 1,), dtype=torch.int64, device=dev)
             _lib.check(lib.ctct_b200_packed_offsets(lx.data_ptr(), ly.data_ptr(), N, max_frames, U1, cu.data_ptr(), st),
@@ -75,7 +76,7 @@ class FusedPackedCTCTLoss(torch.autograd.Function):
             ctx.save_for_backward(buf, packed, cu, labels, lx, ly)
             ctx.meta = (N, max_frames, U1, V, R, red, bool(average_frames), float(norm), bool(from_logits))
             ctx.cleared = grad
-        return out
+        return out[0] if red else out[1:]
 
     @staticmethod
     def backward(ctx, grad_out: T):
@@ -83,11 +84,10 @@ class FusedPackedCTCTLoss(torch.autograd.Function):
         N, Tm, U1, V, R, red, avg, norm, from_logits = ctx.meta
         dev = packed.device
         lib = _lib.lib()
-        # `grad_out` is the gradient of [loss, costs...]: the reduced loss when there is a reduction
-        go = (grad_out[0:1] if red else grad_out[1:]).to(torch.float32).contiguous()
+        go = grad_out.to(torch.float32).contiguous()   # one float for a reduced loss, else N
         out, ctx.cleared = ctx.cleared, None
-        with torch.cuda.device(dev):
-            st = _lib.stream_ptr(dev)
+        with _lib.on_device(dev):
+            st = _lib.raw_stream(dev)
             if from_logits:
                 out = torch.empty_like(packed)
                 rc = lib.ctct_b200_logits_backward_packed(
@@ -140,6 +140,5 @@ def ctct_loss_packed(log_probs: T, labels: T, frames_lengths: T, labels_lengths:
     out = FusedPackedCTCTLoss.apply(log_probs, _as_int(labels), lx, _as_int(labels_lengths), enable_grad, red,
                                     bool(average_frames) and red != 0, norm, int(max_frames), bool(from_logits))
     if red:
-        return out[0]
-    costs = out[1:]
-    return costs / frames_lengths if average_frames else costs
+        return out
+    return out / frames_lengths if average_frames else out
