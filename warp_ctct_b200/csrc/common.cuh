@@ -111,7 +111,7 @@ __device__ __forceinline__ void cp_async_wait() {
 // A slice of a buffer that extra thread blocks of a kernel fill with zeros while the kernel's own
 // blocks do their work.  The dense gradient of the backward pass is all zeros but for <= 3
 // columns per row, and clearing it needs nothing the forward pass computes, so the forward
-// kernels carry its clearing: blocks [first_block, gridDim.x) of a launch clear 1024 16-byte
+// kernels carry its clearing: blocks [first_block, gridDim.x) of a launch clear CLEAR_CHUNK 16-byte
 // vectors each (many short blocks reach the HBM write peak, a persistent grid does not).
 struct ClearSlice {
     uint4 *ptr;                 // nullptr: no clearing in this launch
@@ -121,12 +121,15 @@ struct ClearSlice {
 };
 
 constexpr unsigned CLEAR_TILE_BYTES = 16384;                       // zeroed shared-memory tile
-constexpr unsigned CLEAR_TILES_PER_BLOCK = 16;                     // bulk stores per clearing block
+// Bulk stores per clearing block.  Short blocks win: measured at the benchmark shape (1.09 GB beside 64
+// lattice CTAs) 16 / 32 / 48 / 64 / 96 / 256 / 1024 KB per block give 158.5 / 158.7 / 159.9 / 160.1 /
+// 161.7 / 168.8 / 174.3 us for the launch (tile sizes of 8, 16 and 32 KB make no difference).
+constexpr unsigned CLEAR_TILES_PER_BLOCK = 2;
 constexpr unsigned CLEAR_CHUNK = CLEAR_TILE_BYTES / 16 * CLEAR_TILES_PER_BLOCK;  // 16-byte vectors per block
 
 // Returns true if this block is a clearing block (and has done its clearing).
 // The block zeroes a 16 KB tile of its shared memory once and one thread then streams it out with
-// 1-D bulk (TMA) stores: a handful of instructions per 256 KB, so the clearing hardly touches the
+// 1-D bulk (TMA) stores: a handful of instructions per 32 KB, so the clearing hardly touches the
 // load/store pipes that the kernel's own blocks on the same SM depend on.  `smem` must offer
 // CLEAR_TILE_BYTES (16-byte aligned); with less, plain 16-byte stores are used.
 __device__ __forceinline__ bool clear_role(const ClearSlice &c, void *smem, unsigned smem_bytes) {
