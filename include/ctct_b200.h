@@ -317,6 +317,13 @@ size_t ctct_b200_log_matmul_tc_workspace_bytes(int64_t B, int64_t M, int64_t N, 
  * underflowed.  Either one non-zero means the exact kernels produced the results of the calls
  * that used the workspace; all zero means the tensor-core results stand. */
 size_t ctct_b200_log_matmul_tc_flags_offset(int64_t B, int64_t M, int64_t N, int64_t K);
+/* Test hook (no counterpart in the reference): every wait of the tensor-core kernels (on a TMA load, an
+ * MMA, an epilogue) polls at most `polls` times and then gives up: the thread block raises status word
+ * [0], lets loads it has already issued land, frees its tensor memory and returns, and the exact kernel
+ * launched behind produces the result.  0 makes every wait give up before anything was issued; a negative
+ * value restores the default (2^23 polls).  Synchronous (a copy into constant memory of the current
+ * device); not for use while kernels of this library run. */
+int ctct_b200_debug_set_wait_limit(long long polls);
 int ctct_b200_log_matmul_tc(const float *f, const float *g, int64_t B, int64_t M, int64_t N, int64_t K, float *den,
                             void *workspace, size_t workspace_bytes, void *stream);
 

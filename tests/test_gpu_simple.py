@@ -387,3 +387,47 @@ def test_log_matmul_broadcasts_a_batch_of_one_on_the_right(W):
     torch.logsumexp(c[:, :, None, :] + d[:, None, :, :], -1).backward(go)
     assert b.grad.shape == d.grad.shape == (1, N, K)
     assert (a.grad - c.grad).abs().max().item() < 2e-5 and (b.grad - d.grad).abs().max().item() < 5e-5
+
+
+def test_tensor_core_waits_that_give_up_fall_back_to_the_exact_kernels(W):
+    """Every wait inside the tensor-core kernels is bounded.  With the bound set to zero polls each wait
+    gives up before a single TMA load or MMA was issued: the kernels must raise their status word, free
+    their tensor memory and return, and the exact kernels launched behind them must produce the result.
+    First the forward kernel, then (forward at the normal bound, backward at zero) the backward kernels."""
+    from warp_ctct_b200 import _lib
+    from warp_ctct_b200.simple import log_matmul, log_matmul_tc
+    lib = _lib.lib()
+    rng = np.random.default_rng(77)
+    B, M, N, K = 2, 150, 40, 192
+    f = rng.standard_normal((B, M, K)).astype(np.float32)
+    g = rng.standard_normal((B, N, K)).astype(np.float32)
+    f_t, g_t = _dev(f, g)
+    exact = log_matmul(f_t, g_t.transpose(1, 2))
+    off = lib.ctct_b200_log_matmul_tc_flags_offset(B, M, N, K)
+    try:
+        _lib.check(lib.ctct_b200_debug_set_wait_limit(0), "set_wait_limit")
+        den, ws = log_matmul_tc(f_t, g_t, keep_workspace=True)
+        torch.cuda.synchronize()
+        assert ws[off:off + 4].view(torch.int32).item() == 1, "the give-up status word must be raised"
+        assert torch.equal(den, exact)          # recomputed by the exact kernel inside the same call
+        # backward: planes from a healthy forward pass, every wait of the backward kernels gives up
+        _lib.check(lib.ctct_b200_debug_set_wait_limit(-1), "set_wait_limit")
+        a, b = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+        out = W.LogMMExp.apply(a, b.transpose(1, 2), True, True)
+        ws_bwd = out.grad_fn.saved_tensors[3]
+        assert ws_bwd.numel() > 0 and not ws_bwd[off:off + 16].view(torch.int32).any().item()
+        go = torch.from_numpy(rng.standard_normal((B, M, N)).astype(np.float32)).to(DEV)
+        _lib.check(lib.ctct_b200_debug_set_wait_limit(0), "set_wait_limit")
+        out.backward(go, retain_graph=True)
+        torch.cuda.synchronize()
+        assert ws_bwd[off:off + 4].view(torch.int32).item() == 1
+    finally:
+        _lib.check(lib.ctct_b200_debug_set_wait_limit(-1), "set_wait_limit")
+    c, d = f_t.clone().requires_grad_(True), g_t.clone().requires_grad_(True)
+    torch.logsumexp(c[:, :, None, :] + d[:, None, :, :], -1).backward(go)
+    assert (a.grad - c.grad).abs().max().item() < 2e-5 and (b.grad - d.grad).abs().max().item() < 5e-5
+    # and the library is healthy afterwards: the tensor-core path runs again without raising anything
+    den2, ws2 = log_matmul_tc(f_t, g_t, keep_workspace=True)
+    torch.cuda.synchronize()
+    assert not ws2[off:off + 16].view(torch.int32).any().item()
+    np.testing.assert_allclose(den2.cpu().numpy(), exact.cpu().numpy(), rtol=0, atol=2e-5)

@@ -57,6 +57,7 @@ SIGNATURES = {
     "ctct_b200_export_tables": (_int, [_vp, _sz, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "ctct_b200_log_matmul": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
     "ctct_b200_log_matmul_tc_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64]),
+    "ctct_b200_debug_set_wait_limit": (_int, [C.c_longlong]),
     "ctct_b200_log_matmul_tc_flags_offset": (_sz, [_i64, _i64, _i64, _i64]),
     "ctct_b200_log_matmul_tc": (_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _sz, _vp]),
     "ctct_b200_log_matmul_backward": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),

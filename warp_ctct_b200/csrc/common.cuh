@@ -184,20 +184,30 @@ struct PadClear {
     unsigned row_bytes;        // V * sizeof(element)
     unsigned first_block;
     unsigned slabs;            // N * T
+    unsigned parts;            // blocks per slab: block first_block + slab * parts + p takes bytes [p, p + 1) * PAD_PART_BYTES of the slab
 };
+constexpr unsigned PAD_PART_BYTES = CLEAR_TILE_BYTES * CLEAR_TILES_PER_BLOCK;  // short blocks, as for the flat clearing
 
 // Returns true if this block is a padding-clearing block (and has done its work).  `smem`: at least
 // CLEAR_TILE_BYTES, 16-byte aligned.
 __device__ __forceinline__ bool pad_clear_role(const PadClear &c, void *smem) {
     if (c.out == nullptr || blockIdx.x < c.first_block) return false;
-    const unsigned slab = blockIdx.x - c.first_block;
+    const unsigned idx = blockIdx.x - c.first_block;
+    const unsigned slab = idx / c.parts, part = idx - slab * c.parts;
     if (slab >= c.slabs) return true;
     const int n = static_cast<int>(slab / static_cast<unsigned>(c.T));
     const int t = static_cast<int>(slab - static_cast<unsigned>(n) * c.T);
     const int Un = (t < c.lx[n]) ? min(c.ly[n], c.U1 - 1) : -1;
-    const unsigned long long bytes = static_cast<unsigned long long>(c.U1 - 1 - Un) * c.row_bytes;
-    if (bytes == 0) return true;
-    unsigned char *p = c.out + (static_cast<unsigned long long>(slab) * c.U1 + (Un + 1)) * c.row_bytes;
+    // this block's window of the slab, cut to the slab's padding rows [(Un + 1) * row_bytes, U1 * row_bytes)
+    const unsigned long long slab_bytes = static_cast<unsigned long long>(c.U1) * c.row_bytes;
+    const unsigned long long pad_lo = static_cast<unsigned long long>(Un + 1) * c.row_bytes;
+    unsigned long long lo = static_cast<unsigned long long>(part) * PAD_PART_BYTES;
+    unsigned long long hi = lo + PAD_PART_BYTES;
+    lo = lo < pad_lo ? pad_lo : lo;
+    hi = hi > slab_bytes ? slab_bytes : hi;
+    if (lo >= hi) return true;
+    unsigned char *p = c.out + static_cast<unsigned long long>(slab) * slab_bytes + lo;
+    const unsigned long long bytes = hi - lo;
     const uint4 z = make_uint4(0u, 0u, 0u, 0u);
     uint4 *tile = static_cast<uint4 *>(smem);
     for (unsigned i = threadIdx.x; i < CLEAR_TILE_BYTES / 16; i += blockDim.x) tile[i] = z;

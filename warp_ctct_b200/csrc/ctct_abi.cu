@@ -140,7 +140,7 @@ bool dims_ok(int64_t N, int64_t T, int64_t U1) {
 }
 
 const ClearSlice kNoClear = {nullptr, 0, 0, 0};
-const PadClear kNoPad = {nullptr, nullptr, nullptr, 0, 0, 0, 0, 0};
+const PadClear kNoPad = {nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 1};
 
 // number of clearing blocks a slice adds to a launch
 unsigned clear_blocks(const ClearSlice &c) {
@@ -204,7 +204,8 @@ int launch_lattice(LatticeArgs a, const LatCfg &cfg, int N, cudaStream_t st, Cle
     a.smem_bytes = static_cast<unsigned>(smem);
     a.threads = cfg.threads;
     const unsigned own = static_cast<unsigned>(N) * (a.beta_only ? 1 : 2);
-    const unsigned zero_blocks = pad.out ? pad.slabs : clear_blocks(clear);
+    if (pad.out && static_cast<unsigned long long>(pad.slabs) * pad.parts > 0x7ffffff0ull) return CTCT_ERR_UNSUPPORTED;
+    const unsigned zero_blocks = pad.out ? pad.slabs * pad.parts : clear_blocks(clear);
     clear.first_block = own;
     a.clear = clear;
     pad.first_block = own;
@@ -574,6 +575,7 @@ int forward_impl(const void *log_probs, int dtype, const int32_t *ys, const int3
         pad.U1 = (int)U1;
         pad.row_bytes = static_cast<unsigned>(V * esize);
         pad.slabs = static_cast<unsigned>(N * T);
+        pad.parts = static_cast<unsigned>((static_cast<unsigned long long>(U1) * pad.row_bytes + PAD_PART_BYTES - 1) / PAD_PART_BYTES);
     }
     rc = launch_lattice(make_lattice_args(w, ws, ys, lx, ly, costs, T, U1, want_grad), w.cfg, (int)N, st, cs[1], pad);
     if (rc) return rc;
@@ -978,6 +980,12 @@ int ctct_b200_log_matmul(const float *lhs, int64_t lsb, int64_t lsi, int64_t lsk
 size_t ctct_b200_log_matmul_tc_workspace_bytes(int64_t B, int64_t M, int64_t N, int64_t K) {
     if (!tc_shape_ok(B, M, N, K)) return 0;
     return tc_layout(B, M, N, K).total;
+}
+
+int ctct_b200_debug_set_wait_limit(long long polls) {
+    const unsigned v = polls < 0 ? TC_SPIN_LIMIT : (polls > 0xffffffffLL ? 0xffffffffu : static_cast<unsigned>(polls));
+    if (cudaMemcpyToSymbol(c_tc_spin_limit, &v, sizeof(v)) != cudaSuccess) return check_launch("wait limit");
+    return CTCT_OK;
 }
 
 size_t ctct_b200_log_matmul_tc_flags_offset(int64_t B, int64_t M, int64_t N, int64_t K) {

@@ -39,6 +39,9 @@ constexpr int TC_PLANE_BYTES = TC_BM * TC_BK * 2;                 // 16 KB per o
 constexpr int TC_STAGE_BYTES = 4 * TC_PLANE_BYTES;                // A_hi, A_lo, B_hi, B_lo
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr unsigned TC_SPIN_LIMIT = 1u << 23;                      // polls per wait (a fraction of a second)
+// The limit the kernels actually use: a constant-memory word, so that a test can set it to 0 (every wait
+// gives up before anything was issued) and exercise the give-up paths without hanging anything.
+__constant__ unsigned c_tc_spin_limit = TC_SPIN_LIMIT;
 
 // ---- prologue: row maximum, exp(x - max) split into two bf16 planes -------------------------
 __global__ void __launch_bounds__(256) k_exp_split(const float *__restrict__ x, int K, __nv_bfloat16 *__restrict__ hi,
@@ -94,7 +97,8 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
 }
 // bounded wait on a phase parity (non-blocking polls); false = gave up
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    for (unsigned spin = 0; spin < TC_SPIN_LIMIT; ++spin) {
+    const unsigned limit = c_tc_spin_limit;
+    for (unsigned spin = 0; spin < limit; ++spin) {
         unsigned ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -223,18 +227,25 @@ __global__ void __launch_bounds__(128) k_logmm_tc(const __grid_constant__ CUtens
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer
+        int issued = 0;
         for (int kb = 0; kb < nk && ok; ++kb) {
             const int s = kb % TC_STAGES;
             ok = mbar_wait(empty_bar(s), ((kb / TC_STAGES) & 1) ^ 1);
             if (!ok) break;
             const unsigned st = tiles + s * TC_STAGE_BYTES;
+            issued = kb + 1;
             mbar_expect_tx(full_bar(s), TC_STAGE_BYTES);
             tma_load_3d(st + 0 * TC_PLANE_BYTES, &map_ah, full_bar(s), kb * TC_BK, m0, b);
             tma_load_3d(st + 1 * TC_PLANE_BYTES, &map_al, full_bar(s), kb * TC_BK, m0, b);
             tma_load_3d(st + 2 * TC_PLANE_BYTES, &map_bh, full_bar(s), kb * TC_BK, n0, b);
             tma_load_3d(st + 3 * TC_PLANE_BYTES, &map_bl, full_bar(s), kb * TC_BK, n0, b);
         }
-        if (!ok) atomicExch(a.flags, 1);
+        if (!ok) {
+            atomicExch(a.flags, 1);
+            // loads still in flight must land before this CTA's shared memory goes to the next one:
+            // wait (bounded, like every wait) for the last load of every stage that was armed
+            for (int kb = max(0, issued - TC_STAGES); kb < issued; ++kb) mbar_wait(full_bar(kb % TC_STAGES), (kb / TC_STAGES) & 1);
+        }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: D[128x128, fp32 in TMEM] += A[128x16] * B[128x16]^T, both K-major bf16
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<unsigned>(TC_BN >> 3) << 17) |
