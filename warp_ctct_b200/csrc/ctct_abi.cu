@@ -363,8 +363,13 @@ int launch_logmm(const float *lhs, int64_t lsb, int64_t lsi, int64_t lsk, const 
     a.K = (int)K;
     a.N = (int)N;
     a.run_flags = run_flags;
-    dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 31) / 32), (unsigned)B);
-    launch_pdl(k_logmm_exact, grid, dim3(256), 0, st, a);
+    a.tiles = B * ((M + 31) / 32) * ((N + 31) / 32);
+    // stand-by behind the tensor-core kernel (it returns at once unless a flag is up): two blocks per SM,
+    // which loop over the tiles if they do have to run; a stand-alone call gets one block per tile
+    int64_t blocks = a.tiles;
+    if (run_flags && blocks > 2 * static_cast<int64_t>(sm_count())) blocks = 2 * static_cast<int64_t>(sm_count());
+    if (blocks > 0x7fffffff) blocks = 0x7fffffff;
+    launch_pdl(k_logmm_exact, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, st, a);
     return check_launch("log_matmul");
 }
 
@@ -439,12 +444,16 @@ bool tc_shape_ok(int64_t B, int64_t M, int64_t N, int64_t K) {
 }
 
 template <int VT>
-int launch_logmm_bwd_inst(const LogmmBwdArgs &a, int64_t B, size_t smem, cudaStream_t st) {
+int launch_logmm_bwd_inst(LogmmBwdArgs a, int64_t B, size_t smem, cudaStream_t st) {
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(k_logmm_bwd_exact<VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("log_matmul_backward smem attribute");
-    dim3 grid((unsigned)((a.K + VT - 1) / VT), (unsigned)B);
-    launch_pdl(k_logmm_bwd_exact<VT>, grid, dim3(VT), smem, st, a);
+    a.items = B * ((a.K + VT - 1) / VT);
+    // stand-by behind the tensor-core kernels: one block per SM that loops if it does have to run
+    int64_t blocks = a.items;
+    if (a.run_flags && blocks > static_cast<int64_t>(sm_count())) blocks = sm_count();
+    if (blocks > 0x7fffffff) blocks = 0x7fffffff;
+    launch_pdl(k_logmm_bwd_exact<VT>, dim3(static_cast<unsigned>(blocks)), dim3(VT), smem, st, a);
     return check_launch("log_matmul_backward");
 }
 
@@ -1090,9 +1099,12 @@ int ctct_b200_simple_forward(const float *f, const float *g, const float *den, c
     cudaEvent_t *slot = prof_slot(4);
     prof_mark(slot, 0, st);
     if (c.total > 0) {
-        const int64_t want = (c.total + 255) / 256;
-        const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
-        launch_pdl(k_simple_compose, dim3(static_cast<unsigned>(want < cap ? want : cap)), dim3(256), 0, st, c);
+        const dim3 grid(static_cast<unsigned>((T + COMPOSE_FRAMES - 1) / COMPOSE_FRAMES), static_cast<unsigned>(N));
+        const size_t smem = static_cast<size_t>(U1) * 3 * sizeof(float);
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(k_simple_compose, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+            return check_launch("simple_compose smem attribute");
+        launch_pdl(k_simple_compose, grid, dim3(256), smem, st, c);
         int rc = check_launch("simple_compose");
         if (rc) return rc;
     }

@@ -25,6 +25,7 @@ struct LogmmArgs {
     float *out;  // (B, M, N) contiguous
     int64_t lsb, lsi, lsk, rsb, rsk, rsj;
     int M, K, N;
+    int64_t tiles;         // B * ceil(M/32) * ceil(N/32)
     const int *run_flags;  // optional {a, b}: run only if a or b is non-zero (fallback after the tensor-core kernel)
 };
 
@@ -36,13 +37,18 @@ __global__ void __launch_bounds__(256) k_logmm_exact(const LogmmArgs a) {
     __shared__ float Bs[32][33];  // [k][j]
     pdl_wait();
     if (a.run_flags != nullptr && a.run_flags[0] == 0 && a.run_flags[1] == 0) return;
-    const int b = blockIdx.z;
-    const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // ty in [0,8)
     const float NINF = -__int_as_float(0x7f800000);
+    const bool rhs_k_fast = (a.rsk == 1) || (a.rsj != 1);
+    // tiles are dealt round-robin to the blocks of the grid (one tile per block for a stand-alone call;
+    // a small grid when the kernel is only the stand-by behind the tensor-core kernel)
+    const int tiles_j = (a.N + 31) / 32, tiles_i = (a.M + 31) / 32;
+    for (int64_t tile = blockIdx.x; tile < a.tiles; tile += gridDim.x) {
+    const int b = static_cast<int>(tile / (static_cast<int64_t>(tiles_i) * tiles_j));
+    const int rest = static_cast<int>(tile - static_cast<int64_t>(b) * tiles_i * tiles_j);
+    const int i0 = (rest / tiles_j) * 32, j0 = (rest % tiles_j) * 32;
     const float *lhs = a.lhs + b * a.lsb;
     const float *rhs = a.rhs + b * a.rsb;
-    const bool rhs_k_fast = (a.rsk == 1) || (a.rsj != 1);
 
     float m[4], s[4];
 #pragma unroll
@@ -92,6 +98,8 @@ __global__ void __launch_bounds__(256) k_logmm_exact(const LogmmArgs a) {
         if (gi < a.M && gj < a.N)
             a.out[(static_cast<int64_t>(b) * a.M + gi) * a.N + gj] = (m[r] > NINF) ? m[r] + lg2(s[r]) * LN2F : NINF;
     }
+    __syncthreads();  // the shared tiles are reused by the next tile of this block
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -106,28 +114,70 @@ struct ComposeArgs {
     int64_t total;     // N*T*U1*4
 };
 
+// One block per (utterance, 8 frames), one warp per frame, lanes over the contexts u.
+// What a frame needs from f is one value per LABEL, not three per context: f[t, ys[u]] is the "next
+// label" pick of context u and the "repeat" pick of context u+1, so each lane makes one isolated read
+// and hands it to its neighbour by a shuffle; the picks of g do not depend on the frame at all and are
+// staged once per block in shared memory (3 per context).  A third of the isolated reads of a
+// thread-per-element gather.
+constexpr int COMPOSE_FRAMES = 8;
 __global__ void __launch_bounds__(256) k_simple_compose(const ComposeArgs a) {
+    extern __shared__ float gp[];  // [U1][3] picks of g for this utterance, natural-log units
     pdl_wait();
-    const int U = a.U1 - 1;
-    for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < a.total;
-         e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int k = static_cast<int>(e & 3);
-        const int64_t r = e >> 2;
-        const int u = static_cast<int>(r % a.U1);
-        const int64_t nt = r / a.U1;
-        const int n = static_cast<int>(nt / a.T);
-        float v = 0.0f;
-        const int t = static_cast<int>(nt - static_cast<int64_t>(n) * a.T);
-        if (k < 3 && t < a.lx[n] && u <= a.ly[n]) {
-            int idx = 0;
-            if (k == 1 && u >= 1) idx = a.ys[static_cast<int64_t>(n) * U + u - 1];
-            if (k == 2 && u < a.ly[n]) idx = a.ys[static_cast<int64_t>(n) * U + u];
-            idx = min(max(idx, 0), a.V - 1);
-            float x = __ldg(a.f + nt * a.V + idx) + __ldg(a.g + (static_cast<int64_t>(n) * a.U1 + u) * a.V + idx);
-            if (a.den) x -= __ldg(a.den + nt * a.U1 + u);
-            v = to_log2(x);
+    const int n = blockIdx.y;
+    const int U1 = a.U1, U = U1 - 1;
+    const int Tn = max(0, min(a.lx[n], a.T));
+    const int Un = max(0, min(a.ly[n], U));
+    const int *y = a.ys + static_cast<int64_t>(n) * U;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * COMPOSE_FRAMES + warp;
+    float4 *Gs = reinterpret_cast<float4 *>(a.G) + (static_cast<int64_t>(n) * a.T + t) * U1;
+    if (blockIdx.x * COMPOSE_FRAMES >= Tn) {  // nothing but padding frames in this block
+        if (t < a.T)
+            for (int u = lane; u < U1; u += 32) Gs[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        return;
+    }
+    for (int i = threadIdx.x; i < 3 * (Un + 1); i += 256) {
+        const int u = i / 3, k = i - 3 * u;
+        int idx = 0;
+        if (k == 1 && u >= 1) idx = y[u - 1];
+        if (k == 2 && u < Un) idx = y[u];
+        idx = min(max(idx, 0), a.V - 1);
+        gp[i] = __ldg(a.g + (static_cast<int64_t>(n) * U1 + u) * a.V + idx);
+    }
+    __syncthreads();
+    if (t >= a.T) return;
+    if (t >= Tn) {
+        for (int u = lane; u < U1; u += 32) Gs[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        return;
+    }
+    const float *frow = a.f + (static_cast<int64_t>(n) * a.T + t) * a.V;
+    const float *drow = a.den ? a.den + (static_cast<int64_t>(n) * a.T + t) * U1 : nullptr;
+    const float fb = __ldg(frow);  // blank
+    float carry = fb;              // f[t, ys[u-1]] of the first context of the next group of 32 (context 0: unused)
+    for (int u0 = 0; u0 < U1; u0 += 32) {
+        const int u = u0 + lane;
+        // this lane's label pick: f[t, ys[u]] for u < Un (contexts at and beyond Un emit no next label)
+        float fy = fb;
+        if (u < Un) fy = load_sparse(frow + min(max(y[u], 0), a.V - 1));
+        float fprev = __shfl_up_sync(0xffffffffu, fy, 1);
+        if (lane == 0) fprev = carry;
+        carry = __shfl_sync(0xffffffffu, fy, 31);
+        if (u < U1) {
+            float4 rec = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (u <= Un) {
+                const float d = drow ? __ldg(drow + u) : 0.0f;
+                // same float32 order as csrc/simple.cu:20-26: (f + g) - den
+                float x0 = fb + gp[3 * u], x1 = ((u >= 1) ? fprev : fb) + gp[3 * u + 1], x2 = fy + gp[3 * u + 2];
+                if (drow) {
+                    x0 -= d;
+                    x1 -= d;
+                    x2 -= d;
+                }
+                rec = make_float4(to_log2(x0), to_log2(x1), to_log2(x2), 0.0f);
+            }
+            Gs[u] = rec;
         }
-        a.G[e] = v;
     }
 }
 
@@ -144,6 +194,7 @@ struct LogmmBwdArgs {
     float *grad_lhs;        // (B,M,K) or nullptr
     float *grad_rhsT;       // (B,Nc,K) or nullptr
     int M, Nc, K;
+    int64_t items;          // B * ceil(K / VT), set by the launcher
     const int *run_flags;   // optional {a, b}: run only if a or b is non-zero (fallback after the tensor-core kernels)
 };
 
@@ -155,8 +206,11 @@ __global__ void __launch_bounds__(VT) k_logmm_bwd_exact(const LogmmBwdArgs a) {
     extern __shared__ float sm[];
     pdl_wait();
     if (a.run_flags != nullptr && a.run_flags[0] == 0 && a.run_flags[1] == 0) return;
-    const int b = blockIdx.y;
-    const int k = blockIdx.x * VT + threadIdx.x;
+    // work items (batch entry, block of VT vocabulary entries) are dealt round-robin to the blocks
+    const int kblocks = (a.K + VT - 1) / VT;
+    for (int64_t work = blockIdx.x; work < a.items; work += gridDim.x) {
+    const int b = static_cast<int>(work / kblocks);
+    const int k = static_cast<int>(work - static_cast<int64_t>(b) * kblocks) * VT + threadIdx.x;
     const bool kin = k < a.K;
     float *gT = sm;                                   // [Nc][VT]  rhs tile in log2 units
     float *acc = sm + static_cast<size_t>(a.Nc) * VT;  // [Nc][VT]  grad_rhs accumulators
@@ -200,6 +254,8 @@ __global__ void __launch_bounds__(VT) k_logmm_bwd_exact(const LogmmBwdArgs a) {
     if (a.grad_rhsT && kin)
         for (int j = 0; j < a.Nc; ++j)
             a.grad_rhsT[(static_cast<int64_t>(b) * a.Nc + j) * a.K + k] = acc[j * VT + threadIdx.x];
+    __syncthreads();  // the weight rows in shared memory are reused by the next work item
+    }
 }
 
 // ---------------------------------------------------------------------------------------
