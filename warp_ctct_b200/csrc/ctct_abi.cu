@@ -1365,8 +1365,7 @@ static int simple_backward_impl(const float *grads3, const float *grad_out, cons
         if (rc) return rc;
     }
     if (grad_g) {
-        const int64_t warps = N * U1;
-        launch_pdl(k_simple_patch_g, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, st, p, (int)N);
+        launch_pdl(k_simple_patch_g, dim3((unsigned)((U1 + 31) / 32), (unsigned)N), dim3(256), 0, st, p, (int)N);
         int rc = check_launch("simple_patch_g");
         if (rc) return rc;
     }

@@ -299,35 +299,46 @@ __global__ void __launch_bounds__(256) k_simple_patch_f(const PatchArgs a) {
     if (lane == 0) atomicAdd(row, sc * blank);  // a label equal to the blank index lands here too
 }
 
-// grad_g[n,u,{0, ys[u-1], ys[u]}] += sum_t of the three slots.  One warp per (n,u).
+// grad_g[n,u,{0, ys[u-1], ys[u]}] += sum_t of the three slots.  One block per (utterance, 32 contexts):
+// lanes run along u, so that a warp reads 512 contiguous bytes of records per frame, the 8 warps
+// take the frames round-robin, and their partial sums meet in shared memory (fixed order).
 __global__ void __launch_bounds__(256) k_simple_patch_g(const PatchArgs a, int N) {
+    __shared__ float part[8][32][3];
     pdl_wait();
-    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (w >= N * a.U1) return;
-    const int n = w / a.U1, u = w - n * a.U1;
+    const int n = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int u = blockIdx.x * 32 + lane;
     const int U = a.U1 - 1;
     const int Tn = max(0, min(a.lx[n], a.T)), Un = max(0, min(a.ly[n], U));
-    if (u > Un) return;
+    if (blockIdx.x * 32 > Un) return;
     float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f;
-    for (int t = lane; t < Tn; t += 32) {
-        const float4 g3 = a.grads3[(static_cast<int64_t>(n) * a.T + t) * a.U1 + u];
-        s0 += g3.x;
-        s1 += g3.y;
-        s2 += g3.z;
+    if (u <= Un) {
+        const float4 *g3 = a.grads3 + static_cast<int64_t>(n) * a.T * a.U1 + u;
+        for (int t = warp; t < Tn; t += 8) {
+            const float4 v = g3[static_cast<int64_t>(t) * a.U1];
+            s0 += v.x;
+            s1 += v.y;
+            s2 += v.z;
+        }
     }
+    part[warp][lane][0] = s0;
+    part[warp][lane][1] = s1;
+    part[warp][lane][2] = s2;
+    __syncthreads();
+    if (warp == 0 && u <= Un) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
-    }
-    if (lane == 0) {
+        for (int w = 1; w < 8; ++w) {
+            s0 += part[w][lane][0];
+            s1 += part[w][lane][1];
+            s2 += part[w][lane][2];
+        }
         const float sc = a.scale[n];
         float *row = a.grad_g + (static_cast<int64_t>(n) * a.U1 + u) * a.V;
         row[0] += sc * s0;
         if (u >= 1) row[min(max(a.ys[static_cast<int64_t>(n) * U + u - 1], 0), a.V - 1)] += sc * s1;
         if (u < Un) row[min(max(a.ys[static_cast<int64_t>(n) * U + u], 0), a.V - 1)] += sc * s2;
     }
+    (void)N;
 }
 
 // ---------------------------------------------------------------------------------------
