@@ -402,33 +402,65 @@ __global__ void __launch_bounds__(256) k_zero_fill(uint4 *__restrict__ out, size
     if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < tail_bytes) tail[threadIdx.x] = 0;
 }
 
-// Writes one whole 32-byte sector of a row: zeros except the patched columns that fall into it.
+// One whole 32-byte sector of a row in registers: zeros except the patched columns that fall into it.
 // Whole-sector writes need no read of the old contents, so patching costs DRAM writes only.
+// A sector is built from zeros by dropping each value into its position (one compare and one
+// predicated move per position), not by comparing every column with every patch.
 template <typename OutT>
-__device__ __forceinline__ void write_sector(OutT *row, int sector, const RowPatch<OutT> &p) {
-    constexpr int E = OutOps<OutT>::E;  // elements per 16 bytes
-    uint4 w[2];
+struct SectorWords {
+    static constexpr int ES = 2 * OutOps<OutT>::E;                    // elements per sector
+    static constexpr int PER_WORD = 4 / static_cast<int>(sizeof(OutT));  // elements per 32-bit word
+    unsigned w[8];
+    __device__ __forceinline__ void clear() {
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        unsigned b[E];
+        for (int i = 0; i < 8; ++i) w[i] = 0u;
+    }
+    // element `pos` (0 <= pos < ES) of the sector becomes x; an earlier value at the same position is replaced
+    __device__ __forceinline__ void put(int pos, OutT x) {
+        const unsigned bits = out_bits<OutT>(x);
+        if constexpr (PER_WORD == 1) {
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-            const int col = sector * 2 * E + h * E + e;
-            OutT x = OutOps<OutT>::cvt(0.0f);
-            if (col == 0) x = p.c0;
-            if (col == p.i1) x = p.c1;
-            if (col == p.i2) x = p.c2;
-            b[e] = out_bits<OutT>(x);
-        }
-        if constexpr (E == 4) {
-            w[h] = make_uint4(b[0], b[1], b[2], b[3]);
+            for (int i = 0; i < 8; ++i)
+                if (pos == i) w[i] = bits;
         } else {
-            w[h] = make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16));
+            const int word = pos >> 1;
+            const unsigned shift = (pos & 1) * 16u;
+            const unsigned keep = ~(0xffffu << shift), val = bits << shift;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (word == i) w[i] = (w[i] & keep) | val;
         }
     }
-    uint4 *dst = reinterpret_cast<uint4 *>(row) + sector * 2;
-    dst[0] = w[0];
-    dst[1] = w[1];
+    __device__ __forceinline__ void store(OutT *row, int sector) const {
+        uint4 *dst = reinterpret_cast<uint4 *>(row) + sector * 2;
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+};
+
+// The <= 3 sectors of a row that hold non-zero columns: sector 0 (column 0, plus a label column below
+// the sector width) and the sectors of the two label columns.
+template <typename OutT>
+__device__ __forceinline__ void write_row_sectors(OutT *row, const RowPatch<OutT> &p) {
+    constexpr int ES = SectorWords<OutT>::ES;
+    const int s1 = p.i1 >= 0 ? p.i1 / ES : 0, s2 = p.i2 >= 0 ? p.i2 / ES : 0;
+    SectorWords<OutT> sec;
+    sec.clear();
+    sec.put(0, p.c0);
+    if (p.i1 >= 0 && s1 == 0) sec.put(p.i1, p.c1);
+    if (p.i2 >= 0 && s2 == 0) sec.put(p.i2, p.c2);
+    sec.store(row, 0);
+    if (s1 != 0) {
+        sec.clear();
+        sec.put(p.i1 - s1 * ES, p.c1);
+        if (s2 == s1) sec.put(p.i2 - s2 * ES, p.c2);
+        sec.store(row, s1);
+    }
+    if (s2 != 0 && s2 != s1) {
+        sec.clear();
+        sec.put(p.i2 - s2 * ES, p.c2);
+        sec.store(row, s2);
+    }
 }
 
 // One thread per (n,t,u) row; rows outside t < lx, u <= ly stay zero.  SECTORS: rows start on
@@ -436,7 +468,6 @@ __device__ __forceinline__ void write_sector(OutT *row, int sector, const RowPat
 template <typename OutT, bool SECTORS>
 __global__ void __launch_bounds__(256) k_dense_patch(const DenseArgs a, int64_t rows) {
     pdl_wait();
-    constexpr int ES = 2 * OutOps<OutT>::E;  // elements per 32-byte sector
     const int U = a.U1 - 1, V = a.V;
     for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < rows;
          r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -456,10 +487,7 @@ __global__ void __launch_bounds__(256) k_dense_patch(const DenseArgs a, int64_t 
         if (a.cu && r_out >= a.packed_rows) continue;
         OutT *row = static_cast<OutT *>(a.out) + r_out * V;
         if (SECTORS) {
-            const int s1 = p.i1 >= 0 ? p.i1 / ES : 0, s2 = p.i2 >= 0 ? p.i2 / ES : 0;
-            write_sector<OutT>(row, 0, p);
-            if (s1 != 0) write_sector<OutT>(row, s1, p);
-            if (s2 != 0 && s2 != s1) write_sector<OutT>(row, s2, p);
+            write_row_sectors<OutT>(row, p);
         } else {
             row[0] = p.c0;
             if (p.i1 >= 0) row[p.i1] = p.c1;

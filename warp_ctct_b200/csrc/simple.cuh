@@ -314,7 +314,19 @@ __global__ void __launch_bounds__(256) k_simple_patch_g(const PatchArgs a, int N
     float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f;
     if (u <= Un) {
         const float4 *g3 = a.grads3 + static_cast<int64_t>(n) * a.T * a.U1 + u;
-        for (int t = warp; t < Tn; t += 8) {
+        int t = warp;
+        for (; t + 56 < Tn; t += 64) {  // eight independent loads in flight per lane
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = g3[static_cast<int64_t>(t + 8 * k) * a.U1];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                s0 += v[k].x;
+                s1 += v[k].y;
+                s2 += v[k].z;
+            }
+        }
+        for (; t < Tn; t += 8) {
             const float4 v = g3[static_cast<int64_t>(t) * a.U1];
             s0 += v.x;
             s1 += v.y;
