@@ -734,7 +734,9 @@ def run_b200(args):
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        from warp_ctct_b200.sharded import close_scalar_comms
         dist.barrier()
+        close_scalar_comms()
         dist.destroy_process_group()
     return 0
 
@@ -1040,7 +1042,9 @@ def run_b200_simple(args):
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        from warp_ctct_b200.sharded import close_scalar_comms
         dist.barrier()
+        close_scalar_comms()
         dist.destroy_process_group()
     return 0
 

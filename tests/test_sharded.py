@@ -105,3 +105,23 @@ def test_global_reduction_with_two_gloo_ranks():
         for rank in range(world):
             for key, (ok_value, ok_grad) in out[rank].items():
                 assert ok_value and ok_grad, (rank, key)
+
+
+def test_nccl_entry_points_of_the_scalar_communicator_resolve():
+    """The sharded loss on NCCL groups calls NCCL's C interface directly for its 4-byte all-reduce:
+    the library torch runs on must offer those entry points, and the unique id must have nccl.h's size."""
+    import ctypes
+
+    assert ctypes.sizeof(sharded._NcclUniqueId) == 128
+    lib = sharded._nccl_library()
+    for name in ("ncclGetUniqueId", "ncclCommInitRank", "ncclAllReduce", "ncclCommDestroy", "ncclGetErrorString"):
+        assert hasattr(lib, name), name
+    version = ctypes.c_int()
+    assert lib.ncclGetVersion(ctypes.byref(version)) == 0 and version.value >= 21800
+
+
+def test_cpu_groups_keep_the_process_group_all_reduce():
+    """No communicator of the library's own is made for a tensor that is not a float32 CUDA tensor."""
+    buf = torch.zeros(())
+    assert sharded._async_all_reduce(buf, None) is buf      # one rank: nothing to do
+    assert not sharded._scalar_comms

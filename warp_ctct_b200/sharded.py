@@ -8,6 +8,7 @@ warp_ctct/__init__.py:138-147 applied to the GLOBAL batch.
 from __future__ import annotations
 
 import collections
+import ctypes
 from typing import List, Optional, Sequence
 
 import torch
@@ -36,10 +37,6 @@ def plan_shards(frames_lengths: Sequence[int], labels_lengths: Sequence[int], wo
 
 def shard_weights(frames_lengths, labels_lengths, plan) -> List[int]:
     return [sum(int(frames_lengths[n]) * (int(labels_lengths[n]) + 1) for n in idx) for idx in plan]
-
-
-def _multi_rank(group) -> bool:
-    return dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
 
 
 # ---- the scalar all-reduce, kept off the compute stream -------------------------------------------
@@ -91,11 +88,156 @@ _inflight: collections.deque = collections.deque()
 _MAX_INFLIGHT = 4
 
 
-def _async_all_reduce(buf: torch.Tensor, group) -> "PendingLoss | torch.Tensor":
-    """Start sum-all-reduce of `buf` in place; returns it as a PendingLoss (or as it is with one rank)."""
-    if not _multi_rank(group):
+class _StreamWait:
+    """What PendingLoss.settle() needs of a collective: wait() makes the current stream wait for it."""
+
+    __slots__ = ("event", "device_index")
+
+    def __init__(self, event, device_index):
+        self.event = event
+        self.device_index = device_index
+
+    def wait(self):
+        if torch.cuda.current_device() == self.device_index:
+            self.event.wait()   # the current stream of the current device waits
+        else:
+            torch.cuda.current_stream(self.device_index).wait_event(self.event)
+
+
+class _NcclUniqueId(ctypes.Structure):
+    _fields_ = [("internal", ctypes.c_char * 128)]   # ncclUniqueId of nccl.h
+
+
+def _nccl_library():
+    """The NCCL shared library torch itself runs on (already loaded in this process), with the four
+    entry points of nccl.h this module calls."""
+    lib = ctypes.CDLL("libnccl.so.2")
+    lib.ncclGetErrorString.restype = ctypes.c_char_p
+    lib.ncclGetErrorString.argtypes = [ctypes.c_int]
+    lib.ncclGetUniqueId.argtypes = [ctypes.POINTER(_NcclUniqueId)]
+    lib.ncclCommInitRank.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, _NcclUniqueId, ctypes.c_int]
+    lib.ncclAllReduce.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int,
+                                  ctypes.c_void_p, ctypes.c_void_p]
+    lib.ncclCommDestroy.argtypes = [ctypes.c_void_p]
+    return lib
+
+
+_NCCL_FLOAT32, _NCCL_SUM = 7, 0   # ncclDataType_t / ncclRedOp_t of nccl.h
+
+
+class _ScalarComm:
+    """A communicator of this library's own for the one-float all-reduce of a CUDA process group.
+
+    `torch.distributed.all_reduce` costs 50-100 microseconds of HOST time per call inside a step (work
+    object, watchdog bookkeeping, argument checks, logging wrapper): about half of what it takes to
+    enqueue the whole loss, and enough to make the sharded step host-bound.  The collective itself is
+    four bytes.  So the first sharded call on an NCCL group creates an NCCL communicator over the same
+    ranks through NCCL's C interface (the unique id travels through the process group once) and a
+    communication stream, and every later call is: record an event on the compute stream, make the
+    communication stream wait for it, ncclAllReduce there, record an event behind it."""
+
+    def __init__(self, group, device):
+        self.lib = _nccl_library()
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        uid = _NcclUniqueId()
+        if rank == 0:
+            self._check(self.lib.ncclGetUniqueId(ctypes.byref(uid)), "ncclGetUniqueId")
+        box = [ctypes.string_at(ctypes.addressof(uid), 128) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        ctypes.memmove(ctypes.addressof(uid), box[0], 128)
+        self.comm = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            self._check(self.lib.ncclCommInitRank(ctypes.byref(self.comm), world, uid, rank), "ncclCommInitRank")
+            self.stream = torch.cuda.Stream(device)
+            # Events are recorded again and again instead of created per call.  A wait captures the
+            # record that precedes it, so `ready` can be a single event.  The `done` events form a ring
+            # twice as long as the queue of collectives in flight: the oldest one of the queue still has
+            # its own record when it is settled (waiting for it must not mean waiting for the newest
+            # collective), and whoever holds a handle for longer than a lap waits for a later point of
+            # the same stream, which implies its own.
+            self.ready = torch.cuda.Event()
+            index = torch.device(device).index
+            self.done = [_StreamWait(torch.cuda.Event(), index) for _ in range(2 * (_MAX_INFLIGHT + 1))]
+            self.turn = 0
+        self.device_index = index
+        self.stream_handle = ctypes.c_void_p(self.stream.cuda_stream)
+        self.device = device
+
+    def _check(self, rc: int, what: str) -> None:
+        if rc != 0:
+            raise RuntimeError(f"{what}: {self.lib.ncclGetErrorString(rc).decode()}")
+
+    def all_reduce(self, buf: torch.Tensor) -> _StreamWait:
+        assert buf.dtype == torch.float32 and buf.is_contiguous()
+        if torch.cuda.current_device() == self.device_index:
+            self.ready.record()   # on the current stream
+        else:
+            self.ready.record(torch.cuda.current_stream(self.device))
+        self.stream.wait_event(self.ready)
+        ptr = buf.data_ptr()
+        self._check(self.lib.ncclAllReduce(ptr, ptr, buf.numel(), _NCCL_FLOAT32, _NCCL_SUM, self.comm, self.stream_handle),
+                    "ncclAllReduce")
+        done = self.done[self.turn]
+        self.turn = (self.turn + 1) % len(self.done)
+        done.event.record(self.stream)
+        return done
+
+    def close(self) -> None:
+        if self.comm:
+            self.stream.synchronize()
+            self.lib.ncclCommDestroy(self.comm)
+            self.comm = ctypes.c_void_p()
+
+
+_scalar_comms: dict = {}
+FAST_SCALAR_ALL_REDUCE = True   # False: always go through torch.distributed.all_reduce(async_op=True)
+
+
+def _scalar_comm(group, device):
+    """The _ScalarComm of (group, device), created on first use by ALL ranks of the group together;
+    None when the group is not an NCCL group of CUDA devices (then torch.distributed does the job)."""
+    key = (id(group) if group is not None else 0, device.index)
+    comm = _scalar_comms.get(key, False)
+    if comm is False:
+        comm = None
+        try:
+            if FAST_SCALAR_ALL_REDUCE and device.type == "cuda" and "nccl" in str(dist.get_backend(group)):
+                comm = _ScalarComm(group, device)
+        except Exception as exc:   # e.g. no raw NCCL binding in this torch build: the process group still works
+            import warnings
+            warnings.warn(f"warp_ctct_b200: scalar communicator unavailable ({exc!r}); using torch.distributed.all_reduce")
+            comm = None
+        _scalar_comms[key] = comm
+    return comm
+
+
+def close_scalar_comms() -> None:
+    """Destroys the communicators this module created (every rank calls it, before
+    torch.distributed.destroy_process_group); later sharded calls create new ones."""
+    while _inflight:
+        _inflight.popleft().settle()
+    for comm in _scalar_comms.values():
+        if comm is not None:
+            comm.close()
+    _scalar_comms.clear()
+
+
+def _world_size(group) -> int:
+    return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+
+
+def _async_all_reduce(buf: torch.Tensor, group, world: Optional[int] = None) -> "PendingLoss | torch.Tensor":
+    """Start sum-all-reduce of `buf` in place; returns it as a PendingLoss (or as it is with one rank).
+    `world`: the size of the group where the caller has looked it up already."""
+    if (world if world is not None else _world_size(group)) <= 1:
         return buf
-    work = dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True)
+    comm = None
+    if buf.is_cuda and buf.dtype == torch.float32 and buf.is_contiguous():
+        comm = _scalar_comm(group, buf.device)
+    if comm is not None:
+        work = comm.all_reduce(buf)
+    else:
+        work = dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True)
     out = buf.as_subclass(PendingLoss)
     out._work = work
     _inflight.append(out)
@@ -126,7 +268,7 @@ class _ShardedReducedLoss(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, log_probs, labels, lx, ly, requires_grad: bool, mean: bool, average_frames: bool, norm: float,
-                group, from_logits: bool):
+                group, from_logits: bool, world: int):
         if from_logits:
             from .logits import _forward as fwd
             ctx.from_logits = True
@@ -135,15 +277,15 @@ class _ShardedReducedLoss(torch.autograd.Function):
             ctx.from_logits = False
             loss = _fused_forward(ctx, log_probs, labels, lx, ly, requires_grad, 2 if mean else 1, bool(average_frames),
                                   float(norm))[0]
-        _started.append(_async_all_reduce(loss, group))
+        _started.append(_async_all_reduce(loss, group, world))
         return loss
 
     @staticmethod
     def backward(ctx, grad_loss):
         if ctx.from_logits:
             from .logits import _backward as bwd
-            return bwd(ctx, grad_loss), None, None, None, None, None, None, None, None, None
-        return _fused_backward(ctx, grad_loss), None, None, None, None, None, None, None, None, None
+            return bwd(ctx, grad_loss), None, None, None, None, None, None, None, None, None, None
+        return _fused_backward(ctx, grad_loss), None, None, None, None, None, None, None, None, None, None
 
 
 # side channel from the forward of the two functions above to their caller: the started collective
@@ -207,7 +349,7 @@ def sharded_ctct_loss(log_probs: torch.Tensor, labels: torch.Tensor, frames_leng
     assert log_probs.size(2) == labels.size(1) + 1
     assert log_probs.size(0) == labels.size(0) == frames_lengths.size(0) == labels_lengths.size(0)
     _require_cuda(log_probs=log_probs, ys=labels, lx=frames_lengths, ly=labels_lengths)
-    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    world = _world_size(group)
     if global_batch is None:
         global_batch = log_probs.size(0) * world
     enable_grad = log_probs.requires_grad and torch.is_grad_enabled()
@@ -220,7 +362,7 @@ def sharded_ctct_loss(log_probs: torch.Tensor, labels: torch.Tensor, frames_leng
         # divided by the global batch); the all-reduce of that one float completes it
         return _attach(_ShardedReducedLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths),
                                                  _as_int(labels_lengths), enable_grad, reduction == "mean",
-                                                 bool(average_frames), float(global_batch), group, bool(from_logits)))
+                                                 bool(average_frames), float(global_batch), group, bool(from_logits), world))
     if from_logits:
         from .logits import FusedLogitsCTCTLoss
         costs = FusedLogitsCTCTLoss.apply(log_probs, _as_int(labels), _as_int(frames_lengths), _as_int(labels_lengths),
@@ -244,7 +386,7 @@ def sharded_ctct_simple_loss(f: torch.Tensor, g: torch.Tensor, labels: torch.Ten
     assert g.size(1) == labels.size(1) + 1
     assert f.size(0) == g.size(0) == labels.size(0) == frames_lengths.size(0) == labels_lengths.size(0)
     _require_cuda(f=f, g=g, ys=labels, lx=frames_lengths, ly=labels_lengths)
-    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    world = _world_size(group)
     if global_batch is None:
         global_batch = f.size(0) * world
     track_f = f.requires_grad and torch.is_grad_enabled()
