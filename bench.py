@@ -353,11 +353,12 @@ class Timer:
         enqueue_us = 1e6 * (time.perf_counter() - t_host) / max(n, 1)
         self.ev1.record()
         self.barrier()
-        t = self.torch.tensor([self.ev0.elapsed_time(self.ev1)], device=self.dev)
+        t = self.torch.tensor([self.ev0.elapsed_time(self.ev1), enqueue_us], device=self.dev)
         if self.world > 1:
             import torch.distributed as dist
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()), enqueue_us, out
+        # both figures are the maximum over ranks: the slowest GPU and the slowest host thread set the pace
+        return float(t[0].item()), float(t[1].item()), out
 
     def passes(self, fn, steps, n_passes):
         """R passes of K steps: per-pass ms per step, host enqueue time, last result."""

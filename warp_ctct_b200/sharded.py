@@ -67,6 +67,11 @@ class PendingLoss(torch.Tensor):
         if work is not None:
             work.wait()   # stream wait for NCCL; host wait for gloo
 
+    def backward(self, gradient=None, retain_graph=None, create_graph=False, inputs=None):
+        # straight to autograd, without the detour through __torch_function__ (and without waiting)
+        with torch._C.DisableTorchFunctionSubclass():
+            return torch.Tensor.backward(self, gradient, retain_graph, create_graph, inputs)
+
     @classmethod
     def __torch_function__(cls, func, types, args=(), kwargs=None):
         if getattr(func, "__name__", "") not in _NO_WAIT_NAMES:
@@ -81,11 +86,14 @@ class PendingLoss(torch.Tensor):
             return func(*args, **(kwargs or {}))
 
 
-# Collectives in flight whose buffers must stay alive: (work, tensor).  The oldest is settled when the
-# fifth arrives, by which time it has long completed, so the wait is free and memory is handed back
-# to the allocator only after the communication stream is done with it.
+# Collectives in flight whose buffers must stay alive until the communication stream is done with
+# them.  A finished one is dropped after a look at its state from the host (no operation goes into the
+# compute stream: a wait or a record between two kernels of the loss costs their programmatic overlap,
+# a few microseconds each).  The host may run a few hundred kernels ahead of the GPU, so "still running"
+# is the normal state of the newest entries; only when _MAX_INFLIGHT of them are, is the oldest one
+# waited for on the stream, so that the queue stays bounded (a buffer is 4 bytes).
 _inflight: collections.deque = collections.deque()
-_MAX_INFLIGHT = 4
+_MAX_INFLIGHT = 256
 
 
 class _StreamWait:
@@ -96,6 +104,9 @@ class _StreamWait:
     def __init__(self, event, device_index):
         self.event = event
         self.device_index = device_index
+
+    def is_completed(self) -> bool:
+        return self.event.query()
 
     def wait(self):
         if torch.cuda.current_device() == self.device_index:
@@ -151,13 +162,13 @@ class _ScalarComm:
             self.stream = torch.cuda.Stream(device)
             # Events are recorded again and again instead of created per call.  A wait captures the
             # record that precedes it, so `ready` can be a single event.  The `done` events form a ring
-            # twice as long as the queue of collectives in flight: the oldest one of the queue still has
-            # its own record when it is settled (waiting for it must not mean waiting for the newest
+            # longer than the queue of collectives in flight: the oldest one of the queue still has
+            # its own record when it is looked at (waiting for it must not mean waiting for the newest
             # collective), and whoever holds a handle for longer than a lap waits for a later point of
             # the same stream, which implies its own.
             self.ready = torch.cuda.Event()
             index = torch.device(device).index
-            self.done = [_StreamWait(torch.cuda.Event(), index) for _ in range(2 * (_MAX_INFLIGHT + 1))]
+            self.done = [_StreamWait(torch.cuda.Event(), index) for _ in range(_MAX_INFLIGHT + 8)]
             self.turn = 0
         self.device_index = index
         self.stream_handle = ctypes.c_void_p(self.stream.cuda_stream)
@@ -226,24 +237,39 @@ def _world_size(group) -> int:
     return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
 
 
-def _async_all_reduce(buf: torch.Tensor, group, world: Optional[int] = None) -> "PendingLoss | torch.Tensor":
-    """Start sum-all-reduce of `buf` in place; returns it as a PendingLoss (or as it is with one rank).
-    `world`: the size of the group where the caller has looked it up already."""
+def _start_all_reduce(buf: torch.Tensor, group, world: Optional[int] = None):
+    """Starts the sum-all-reduce of `buf` in place.  Returns the handle of the collective (wait(),
+    is_completed()), or None with one rank.  `world`: the size of the group where the caller has
+    looked it up already."""
     if (world if world is not None else _world_size(group)) <= 1:
-        return buf
+        return None
     comm = None
     if buf.is_cuda and buf.dtype == torch.float32 and buf.is_contiguous():
         comm = _scalar_comm(group, buf.device)
     if comm is not None:
-        work = comm.all_reduce(buf)
-    else:
-        work = dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True)
-    out = buf.as_subclass(PendingLoss)
-    out._work = work
-    _inflight.append(out)
-    while len(_inflight) > _MAX_INFLIGHT:
-        _inflight.popleft().settle()
-    return out
+        return comm.all_reduce(buf)
+    return dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True)
+
+
+def _pending(out: torch.Tensor, handle) -> torch.Tensor:
+    """`out` (what autograd returned for the buffer whose all-reduce `handle` stands for) as a
+    PendingLoss that owns the handle; enters it into the queue of collectives in flight."""
+    if handle is None:
+        return out
+    res = out.as_subclass(PendingLoss)
+    res._work = handle
+    queue = _inflight
+    while queue and (queue[0]._work is None or queue[0]._work.is_completed()):
+        queue.popleft()
+    queue.append(res)   # shares its storage with the buffer: keeps it alive
+    while len(queue) > _MAX_INFLIGHT:
+        queue.popleft().settle()
+    return res
+
+
+def _async_all_reduce(buf: torch.Tensor, group, world: Optional[int] = None) -> torch.Tensor:
+    """Sum-all-reduce of `buf` in place, asynchronously: returns it as a PendingLoss (or as it is with one rank)."""
+    return _pending(buf, _start_all_reduce(buf, group, world))
 
 
 class _AllReduceSum(torch.autograd.Function):
@@ -253,7 +279,7 @@ class _AllReduceSum(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: torch.Tensor, group):
         y = x.clone()
-        _started.append(_async_all_reduce(y, group))
+        _started.append(_start_all_reduce(y, group))
         return y
 
     @staticmethod
@@ -277,7 +303,7 @@ class _ShardedReducedLoss(torch.autograd.Function):
             ctx.from_logits = False
             loss = _fused_forward(ctx, log_probs, labels, lx, ly, requires_grad, 2 if mean else 1, bool(average_frames),
                                   float(norm))[0]
-        _started.append(_async_all_reduce(loss, group, world))
+        _started.append(_start_all_reduce(loss, group, world))
         return loss
 
     @staticmethod
@@ -288,26 +314,15 @@ class _ShardedReducedLoss(torch.autograd.Function):
         return _fused_backward(ctx, grad_loss), None, None, None, None, None, None, None, None, None, None
 
 
-# side channel from the forward of the two functions above to their caller: the started collective
+# side channel from the forward of the two functions above to their caller: the handle of the collective
+# that was started on the tensor they return (autograd hands back a new Python object for that tensor)
 _started: list = []
 
 
 def _attach(out: torch.Tensor) -> torch.Tensor:
-    """`out` is what autograd returned for a tensor whose all-reduce was just started: give it the
-    pending handle (autograd may have wrapped the tensor in a new Python object)."""
-    pending = _started.pop() if _started else None
+    handle = _started.pop() if _started else None
     _started.clear()
-    if not isinstance(pending, PendingLoss):
-        return out
-    if out is pending:
-        return out
-    res = out.as_subclass(PendingLoss)
-    res._work, pending._work = pending._work, None
-    # the queue keeps the object that owns the handle
-    for i, q in enumerate(_inflight):
-        if q is pending:
-            _inflight[i] = res
-    return res
+    return _pending(out, handle)
 
 
 def all_reduce_sum(x: torch.Tensor, group=None) -> torch.Tensor:
