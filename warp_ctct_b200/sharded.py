@@ -148,11 +148,22 @@ class _ScalarComm:
     communication stream wait for it, ncclAllReduce there, record an event behind it."""
 
     def __init__(self, group, device):
-        self.lib = _nccl_library()
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         uid = _NcclUniqueId()
-        if rank == 0:
-            self._check(self.lib.ncclGetUniqueId(ctypes.byref(uid)), "ncclGetUniqueId")
+        # Every rank must take the same road.  What can fail on one rank alone (loading the library,
+        # making the id) happens first, and the ranks agree on the outcome through the process group
+        # before any of them enters NCCL's own collective initialisation.
+        failure = None
+        try:
+            self.lib = _nccl_library()
+            if rank == 0:
+                self._check(self.lib.ncclGetUniqueId(ctypes.byref(uid)), "ncclGetUniqueId")
+        except Exception as exc:
+            failure = exc
+        ok = torch.tensor([0 if failure else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            raise RuntimeError(f"not available on every rank ({failure!r} here)")
         box = [ctypes.string_at(ctypes.addressof(uid), 128) if rank == 0 else None]
         dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
         ctypes.memmove(ctypes.addressof(uid), box[0], 128)
