@@ -9,7 +9,10 @@
 //     same bytes, the MN-major (transposed) A operand of GEMM 2;
 //   * the Ef tile is the B operand of GEMM 2 and, read back by the epilogue threads as hi + lo, the
 //     factor Ef of grad_f, so f is never read; the finished fp32 tile of grad_f is written over the
-//     Ef tile (same number of bytes) and leaves through one TMA store.
+//     lo planes of the P tile (free once both GEMMs are done, same number of bytes) and leaves
+//     through one TMA store.  So the Ef part of a stage goes back to the producer as soon as the
+//     epilogue threads have read it and the hi planes of P as soon as the MMAs are done; only the
+//     load of the next lo planes of P (32 KB out of L2) has to wait for the store.
 // Eg (128 u x 64 v, hi + lo) stays resident for the item as B operand of GEMM 1; grad_g is finished
 // by the epilogue threads straight from / to global memory (it is a tenth of the traffic).
 // HBM traffic: Ef planes read once, grad_f written once, g and grad_g once.
@@ -62,14 +65,16 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
     const unsigned eg = ring + FU_STAGES * FU_STAGE_BYTES;
     const unsigned bars = eg + FU_EG_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };              // stage loaded
-    auto empty_bar = [&](int s) { return bars + 8u * (2 + s); };       // Ef part free again (its store has read it)
-    auto p_empty = [&](int s) { return bars + 8u * (14 + s); };        // P part free again (both GEMMs complete)
+    auto empty_bar = [&](int s) { return bars + 8u * (2 + s); };       // Ef part free again (the epilogue has read it)
+    auto p_hi_empty = [&](int s) { return bars + 8u * (14 + s); };     // hi planes of P free again (both GEMMs complete)
+    auto p_lo_empty = [&](int s) { return bars + 8u * (16 + s); };     // lo planes of P free again (both GEMMs complete AND
+                                                                       // the store of the grad_f tile written over them has read it)
     auto done_bar = [&](int s) { return bars + 8u * (4 + s); };        // both GEMMs of the stage complete
     auto ready_bar = [&](int s) { return bars + 8u * (6 + s); };       // grad_f tile written, store may go
     auto d1_empty = [&](int q) { return bars + 8u * (8 + q); };        // accumulator of GEMM 1 read out
     const unsigned eg_full = bars + 8u * 10, eg_empty = bars + 8u * 11;
     const unsigned d2_full = bars + 8u * 12, d2_empty = bars + 8u * 13;
-    constexpr int NBARS = 16;
+    constexpr int NBARS = 18;
     const unsigned slot_addr = bars + 8u * NBARS;
     unsigned *slot_ptr = reinterpret_cast<unsigned *>(fu_raw + (slot_addr - raw));
     unsigned char *ring_ptr = fu_raw + (ring - raw);
@@ -79,8 +84,9 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
     constexpr unsigned TMEM_COLS = 256;  // D1[0] at 0, D1[1] at 64, D2 at 128
 
     if (threadIdx.x == 0) {
-        // full: two arrivals (P loads, Ef loads); d2_empty: one per epilogue warp
-        for (int q = 0; q < NBARS; ++q) mbar_init(bars + 8u * q, q == 13 ? BW_EPI_WARPS : (q < 2 ? 2 : 1));
+        // full: three arrivals (Ef loads, P hi loads, P lo loads); p_lo_empty: two (MMA commit, store thread);
+        // d2_empty: one per epilogue warp
+        for (int q = 0; q < NBARS; ++q) mbar_init(bars + 8u * q, q == 13 ? BW_EPI_WARPS : (q < 2 ? 3 : (q >= 16 ? 2 : 1)));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -118,31 +124,38 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
             for (int tb = 0; tb < ntb; ++tb, ++tbc) {
                 const int s = tbc & 1;
                 const unsigned ph = (tbc >> 1) & 1;
-                // the P part comes back as soon as the MMAs that read it are done, the Ef part (which
-                // the grad_f tile is written over) only when its store has read it
+                // the Ef part comes back as soon as the epilogue threads have read it, the hi planes of P when the
+                // MMAs are done, the lo planes (which the grad_f tile is written over) when the store has read them
                 const unsigned st = ring + s * FU_STAGE_BYTES;
                 const unsigned bar = full_bar(s);
                 const int t0 = tb * FU_T;
-                ok = mbar_wait(p_empty(s), ph ^ 1);
-                if (!ok) break;
-                mbar_expect_tx(bar, FU_P_BYTES);
-                tma_load_3d(st, &map_ph, bar, 0, t0, b);
-                tma_load_3d(st + BW_A_PLANE, &map_ph, bar, 64, t0, b);
-                tma_load_3d(st + 2 * BW_A_PLANE, &map_pl, bar, 0, t0, b);
-                tma_load_3d(st + 3 * BW_A_PLANE, &map_pl, bar, 64, t0, b);
-                armed |= 1u << s;
-                armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
                 ok = mbar_wait(empty_bar(s), ph ^ 1);
-                if (!ok) {
-                    mbar_expect_tx(bar, 0);  // second arrival of the phase, so that the P loads can be waited for
-                    break;
-                }
+                if (!ok) break;
                 mbar_expect_tx(bar, FU_E_BYTES);
                 const unsigned ef = st + FU_P_BYTES;
                 tma_load_3d(ef, &map_fh, bar, v0, t0, b);
                 tma_load_3d(ef + BW_A_PLANE / 2, &map_fh, bar, v0, t0 + 64, b);
                 tma_load_3d(ef + BW_A_PLANE, &map_fl, bar, v0, t0, b);
                 tma_load_3d(ef + BW_A_PLANE + BW_A_PLANE / 2, &map_fl, bar, v0, t0 + 64, b);
+                armed |= 1u << s;
+                armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+                ok = mbar_wait(p_hi_empty(s), ph ^ 1);
+                if (!ok) {
+                    mbar_expect_tx(bar, 0);  // the missing arrivals of the phase, so that the Ef loads can be waited for
+                    mbar_expect_tx(bar, 0);
+                    break;
+                }
+                mbar_expect_tx(bar, FU_P_BYTES / 2);
+                tma_load_3d(st, &map_ph, bar, 0, t0, b);
+                tma_load_3d(st + BW_A_PLANE, &map_ph, bar, 64, t0, b);
+                ok = mbar_wait(p_lo_empty(s), ph ^ 1);
+                if (!ok) {
+                    mbar_expect_tx(bar, 0);
+                    break;
+                }
+                mbar_expect_tx(bar, FU_P_BYTES / 2);
+                tma_load_3d(st + 2 * BW_A_PLANE, &map_pl, bar, 0, t0, b);
+                tma_load_3d(st + 3 * BW_A_PLANE, &map_pl, bar, 64, t0, b);
             }
         }
         if (!ok) atomicExch(a.flags, 1);
@@ -206,7 +219,8 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
                     umma_bf16(d2, al, bh, idesc2, 1u);
                 }
                 umma_commit(done_bar(s));
-                umma_commit(p_empty(s));
+                umma_commit(p_hi_empty(s));
+                umma_commit(p_lo_empty(s));
                 if (tb == ntb - 1) umma_commit(d2_full);
             }
         }
@@ -273,9 +287,11 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
                 unsigned d[32];
                 tmem_ld_32x32(tmem_base + (static_cast<unsigned>(part * 32) << 16) + q * FU_V + c * 32, d);
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                // every thread has read its part of the Ef tile: the grad_f tile may be written over it
+                // every thread has read its part of the Ef tile: the producer may load the next one into it
                 asm volatile("bar.sync 2, %0;" ::"n"(32 * BW_EPI_WARPS) : "memory");
-                unsigned char *orow = ef + c * BW_A_PLANE + r * 128;  // column half c of the fp32 tile
+                if (leader) mbar_arrive(empty_bar(s));
+                // the grad_f tile goes over the lo planes of the P tile (both GEMMs that read them are complete)
+                unsigned char *orow = ring_ptr + s * FU_STAGE_BYTES + (2 + c) * BW_A_PLANE + r * 128;  // column half c of the fp32 tile
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     float4 o;
@@ -322,8 +338,8 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
         }
         if (!ok && lane == 0) atomicExch(a.flags, 1);
     } else if (warp == 2 + BW_EPI_WARPS && lane == 0) {
-        // ---- store thread: one TMA store per finished grad_f tile; the stage goes back to the producer
-        // as soon as the store has read it
+        // ---- store thread: one TMA store per finished grad_f tile; the P part of the stage goes back to
+        // the producer as soon as the store has read it
         unsigned tbc = 0;
         for (int item = blockIdx.x; item < a.items && ok; item += gridDim.x) {
             int v0, b;
@@ -332,12 +348,12 @@ __global__ void __launch_bounds__(FU_THREADS, 1) k_den_bwd_fused(const __grid_co
                 const int s = tbc & 1;
                 ok = mbar_wait(ready_bar(s), (tbc >> 1) & 1);
                 if (!ok) break;
-                const unsigned ef = ring + s * FU_STAGE_BYTES + FU_P_BYTES;
-                tma_store_3d(&map_out, ef, v0, tb * FU_T, b);
-                tma_store_3d(&map_out, ef + BW_A_PLANE, v0 + 32, tb * FU_T, b);
+                const unsigned tile = ring + s * FU_STAGE_BYTES + 2 * BW_A_PLANE;
+                tma_store_3d(&map_out, tile, v0, tb * FU_T, b);
+                tma_store_3d(&map_out, tile + BW_A_PLANE, v0 + 32, tb * FU_T, b);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                mbar_arrive(empty_bar(s));
+                mbar_arrive(p_lo_empty(s));
             }
         }
         asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
