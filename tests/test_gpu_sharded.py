@@ -37,10 +37,10 @@ def _rank(rank, world, port, out):
         lp, ys, lx, ly = make_case(G, T, U1, V, 1.5, 77, lx_range=(30, 64), ly_range=(3, 16), cap_half=True)
         mine = np.array(plan_shards(lx, ly, world)[rank])
         d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
-        xa = d(lp).requires_grad_(True)          # the whole batch on this GPU
-        ref = W.ctct_loss(xa, d(ys), d(lx), d(ly), reduction="mean")
-        ref.backward()
         for from_logits in (False, True):
+            xa = d(lp).requires_grad_(True)      # the whole batch on this GPU
+            ref = (W.ctct_loss_from_logits if from_logits else W.ctct_loss)(xa, d(ys), d(lx), d(ly), reduction="mean")
+            ref.backward()
             x = d(lp[mine]).requires_grad_(True)
             loss = sharded_ctct_loss(x, d(ys[mine]), d(lx[mine]), d(ly[mine]), global_batch=G, reduction="mean",
                                      from_logits=from_logits)
