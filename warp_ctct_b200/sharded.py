@@ -43,9 +43,10 @@ def shard_weights(frames_lengths, labels_lengths, plan) -> List[int]:
 #
 # The backward pass of a shard needs nothing from the other ranks: the gradient scale is the local
 # utterance weight times the upstream gradient.  Only the VALUE of the reduced loss depends on the
-# collective.  So the all-reduce is issued asynchronously (on the communication stream of the
-# process group, ordered after the kernel that produced this rank's share) and the compute stream
-# waits for it only when somebody looks at the value: `loss.item()`, printing, arithmetic on it.
+# collective.  So the all-reduce is issued asynchronously (on a communication stream, ordered after
+# the kernel that produced this rank's share: the library's own communicator on NCCL groups, see
+# _ScalarComm, else the process group with async_op) and the compute stream waits for it only when
+# somebody looks at the value: `loss.item()`, printing, arithmetic on it.
 # `loss.backward()` does not, so the backward kernels of this step and the forward kernels of the
 # next one run while the 4 bytes travel.
 
@@ -120,7 +121,7 @@ class _NcclUniqueId(ctypes.Structure):
 
 
 def _nccl_library():
-    """The NCCL shared library torch itself runs on (already loaded in this process), with the four
+    """The NCCL shared library torch itself runs on (already loaded in this process), with the
     entry points of nccl.h this module calls."""
     lib = ctypes.CDLL("libnccl.so.2")
     lib.ncclGetErrorString.restype = ctypes.c_char_p
