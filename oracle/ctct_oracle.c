@@ -122,8 +122,10 @@ int oracle_table_f64(const float *g3, int su, const int *ys, int T, int U, int w
 /* Batch forward of the reference's extension entry point ctct_loss_fwd
  * (csrc/binding.cpp:31-100): costs[n] = -betas[n,0,0]; when want_grad, grads =
  * occupancy gradient w.r.t. the gathered log-probs, zeros outside t<lx, u<=ly.
- * An utterance with lx < ly or ly < 1 has no alignment: cost +inf, zero gradient
- * (the reference leaves that case undefined). */
+ * Where the reference leaves the result undefined: an utterance with lx < ly has no alignment
+ * (cost +inf, zero gradient); one without labels (ly == 0) has exactly one, all blanks at
+ * context 0 (cost = minus the sum of those log-probs, gradient -1 on each of them; its table
+ * in ref_ctct.py:6-36 never sets the cell it reads the likelihood from). */
 #define DEFINE_CTCT_FWD(REAL, SFX)                                                               \
     int oracle_ctct_fwd_##SFX(const float *g3, const int *ys, const int *lx, const int *ly,      \
                               int N, int T, int U1, int want_grad, REAL *costs, REAL *grads,     \
@@ -133,6 +135,14 @@ int oracle_table_f64(const float *g3, int su, const int *ys, int T, int U, int w
         if (want_grad) memset(grads, 0, sizeof(REAL) * (size_t)N * T * U1 * 3);                  \
         _Pragma("omp parallel for schedule(dynamic)") for (int n = 0; n < N; ++n) {              \
             const int Tn = lx[n], Un = ly[n];                                                    \
+            if (Un == 0 && Tn >= 0 && Tn <= T) {                                                 \
+                REAL s = 0;                                                                      \
+                for (int t = 0; t < Tn; ++t) s += (REAL)g3[(((size_t)n * T + t) * U1) * 3];      \
+                costs[n] = -s;                                                                   \
+                if (want_grad && isfinite((double)s))                                            \
+                    for (int t = 0; t < Tn; ++t) grads[(((size_t)n * T + t) * U1) * 3] = (REAL)-1; \
+                continue;                                                                        \
+            }                                                                                    \
             if (Tn > T || Un > U1 - 1 || Tn < Un || Un < 1) {                                    \
                 costs[n] = INFINITY;                                                             \
                 continue;                                                                        \

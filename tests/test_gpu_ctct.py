@@ -190,9 +190,11 @@ def test_edge_lengths(W):
     c64, g64 = oracle.ctct_fwd(g3[1:3], ys[1:3], lx[1:3], ly[1:3], True, np.float64)
     np.testing.assert_allclose(res["costs"][1:3], c64, rtol=1e-5)
     assert np.abs(res["grads"][1:3] - g64).max() < 2e-5
-    # no labels: the only path is all blanks (the reference leaves ly = 0 undefined)
+    # no labels: the only path is all blanks (the reference leaves ly = 0 undefined; the oracle defines it the same way)
     assert abs(res["costs"][3] - (-g3[3, :6, 0, 0].sum())) < 1e-4
     np.testing.assert_allclose(res["grads"][3, :6, 0, 0], -1.0, atol=1e-5)
+    c64, g64 = oracle.ctct_fwd(g3[3:4], ys[3:4], lx[3:4], ly[3:4], True, np.float64)
+    assert abs(res["costs"][3] - c64[0]) < 1e-4 and np.abs(res["grads"][3] - g64[0]).max() < 1e-5
     assert np.isposinf(res["costs"][4]) and np.isposinf(res["costs"][5])
     assert not res["grads"][4].any() and not res["grads"][5].any()
     assert res["costs"][6] == 0.0 and not res["grads"][6].any()

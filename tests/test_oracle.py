@@ -130,6 +130,26 @@ def test_ragged_batch_equals_per_utterance():
         assert not dense[n, lx[n]:].any() and not dense[n, :, ly[n] + 1:].any()
 
 
+def test_utterance_without_labels_is_the_all_blank_path():
+    """ly == 0 (undefined in the reference, whose table never sets the cell its likelihood is read from): the one
+    alignment emits a blank at context 0 in every frame; lx == 0 as well: the empty product, cost 0."""
+    rng = np.random.default_rng(5)
+    N, T, U1, V = 4, 7, 4, 6
+    x = rng.standard_normal((N, T, U1, V)).astype(np.float32)
+    lp = x - np.log(np.exp(x).sum(-1, keepdims=True))
+    ys = rng.integers(1, V, (N, U1 - 1)).astype(np.int32)
+    lx = np.array([7, 3, 0, 5], np.int32)
+    ly = np.array([0, 0, 0, 2], np.int32)
+    lp[1, 1, 0, 0] = -np.inf            # a forbidden blank: no alignment left
+    go = np.array([1.0, 1.0, 1.0, 0.5], np.float32)
+    costs, dense = oracle.ctct_loss(lp, ys, lx, ly, go)
+    assert abs(costs[0] + lp[0, :7, 0, 0].sum()) < 1e-5 and np.isposinf(costs[1]) and costs[2] == 0.0
+    assert np.array_equal(dense[0, :, 0, 0], -np.ones(7, np.float32)) and np.abs(dense[0]).sum() == 7.0
+    assert not dense[1].any() and not dense[2].any()
+    c64, g64 = oracle.ctct_fwd(oracle.collect_units(lp, ys), ys, lx, ly, True, np.float64)
+    assert abs(c64[0] - costs[0]) < 1e-5 and abs(c64[3] - costs[3]) < 1e-5 and g64[0, :, 0, 0].tolist() == [-1.0] * 7
+
+
 def test_round_half_matches_numpy():
     rng = np.random.default_rng(5)
     xs = np.concatenate([rng.standard_normal(2000) * 10.0 ** rng.integers(-9, 5, 2000), [0.0, 65504.0, 65519.9, 65520.0, 1e-8, -3e-8]])
