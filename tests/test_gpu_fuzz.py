@@ -94,3 +94,41 @@ def test_random_problems_against_the_oracle(W, seed):
             assert np.abs(got_l[okl] - c_ref[okl]).max() < 3e-4 * max(1.0, float(np.abs(c_ref[okl]).max())), tag
             err = np.abs(np.where(okl[:, None, None, None], xl.grad.float().cpu().numpy() - g_ref, 0.0)).max()
             assert err < TOL[dtype], tag
+
+
+@pytest.mark.parametrize("seed", [21, 22])
+def test_random_simple_loss_problems_against_the_oracle(W, seed):
+    """The log-add joiner on random shapes: vocabularies on both sides of what the tensor-core kernels take
+    (V >= 64 and a multiple of 8), with and without the denominator, against the float64 oracle."""
+    rng = np.random.default_rng(seed)
+    for case in range(40):
+        N, T, U1 = int(rng.integers(1, 5)), int(rng.integers(1, 70)), int(rng.integers(1, 40))
+        V = int(rng.choice([2, 5, 13, 32, 64, 72, 100, 128, 136, 256]))
+        sigma = float(rng.choice([0.5, 1.5, 3.0]))
+        f = (sigma * rng.standard_normal((N, T, V))).astype(np.float32)
+        g = (sigma * rng.standard_normal((N, U1, V))).astype(np.float32)
+        ys = rng.integers(1, V, (N, max(U1 - 1, 0))).astype(np.int32)
+        if U1 > 2 and rng.random() < 0.5:
+            for n in range(N):
+                for u in range(1, U1 - 1):
+                    if rng.random() < 0.4:
+                        ys[n, u] = ys[n, u - 1]
+        lx = rng.integers(1, T + 1, N).astype(np.int32)
+        ly = np.minimum(rng.integers(0, U1, N), lx // 2).astype(np.int32)
+        go = rng.uniform(0.3, 1.5, N).astype(np.float32)
+        normalized = bool(rng.random() < 0.7)
+        tag = (seed, case, (N, T, U1, V), normalized)
+        f_t, g_t = _dev(f).requires_grad_(True), _dev(g).requires_grad_(True)
+        costs = W.ctct_simple_loss(f_t, g_t, _dev(ys), _dev(lx), _dev(ly), reduction="none", normalized=normalized)
+        costs.backward(_dev(go))
+        c_ref, gf_ref, gg_ref = oracle.simple_loss(f, g, ys, lx, ly, normalized, go, dtype=np.float64)
+        ok = np.isfinite(c_ref)
+        got = costs.detach().cpu().numpy()
+        assert (np.isfinite(got) == ok).all(), tag
+        if ok.any():
+            assert np.abs(got[ok] - c_ref[ok]).max() < 2e-5 * max(1.0, float(np.abs(c_ref[ok]).max())), tag
+        okb = ok[:, None, None]
+        # sums of up to T*(U+1) occupancies: 1e-4 absolute + 2e-5 relative, as in test_gpu_simple.py
+        err_f = np.abs(np.where(okb, f_t.grad.cpu().numpy() - gf_ref, 0.0)) - 2e-5 * np.abs(gf_ref)
+        err_g = np.abs(np.where(okb, g_t.grad.cpu().numpy() - gg_ref, 0.0)) - 2e-5 * np.abs(gg_ref)
+        assert err_f.max() < 1e-4 and err_g.max() < 1e-4, tag
