@@ -52,7 +52,7 @@ def _rank(rank, world, port, out):
             res[f"value from_logits={from_logits}"] = abs(value - ref.item()) < 1e-5 * abs(ref.item())
             res[f"grad from_logits={from_logits}"] = (x.grad - xa.grad[mine]).abs().max().item() < 1e-6
             res[f"pending from_logits={from_logits}"] = pending and still and settled
-        res["own communicator"] = any(isinstance(c, sharded._ScalarComm) for c in sharded._scalar_comms.values())
+        res["own communicator"] = any(isinstance(c, sharded._ScalarComm) for c, _ in sharded._scalar_comms.values())
         losses = []
         for _ in range(300):                       # more steps than the event ring is long
             x = d(lp[mine]).requires_grad_(True)

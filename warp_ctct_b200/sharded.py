@@ -219,9 +219,10 @@ FAST_SCALAR_ALL_REDUCE = True   # False: always go through torch.distributed.all
 def _scalar_comm(group, device):
     """The _ScalarComm of (group, device), created on first use by ALL ranks of the group together;
     None when the group is not an NCCL group of CUDA devices (then torch.distributed does the job)."""
-    key = (id(group) if group is not None else 0, device.index)
-    comm = _scalar_comms.get(key, False)
-    if comm is False:
+    pg = group if group is not None else dist.group.WORLD   # the default group is a new object after a re-init
+    key = (id(pg), device.index)
+    comm, owner = _scalar_comms.get(key, (False, None))
+    if comm is False or owner is not pg:   # `owner` keeps the group object alive, so its id is not handed out again
         comm = None
         try:
             if FAST_SCALAR_ALL_REDUCE and device.type == "cuda" and "nccl" in str(dist.get_backend(group)):
@@ -230,7 +231,7 @@ def _scalar_comm(group, device):
             import warnings
             warnings.warn(f"warp_ctct_b200: scalar communicator unavailable ({exc!r}); using torch.distributed.all_reduce")
             comm = None
-        _scalar_comms[key] = comm
+        _scalar_comms[key] = (comm, pg)
     return comm
 
 
@@ -239,7 +240,7 @@ def close_scalar_comms() -> None:
     torch.distributed.destroy_process_group); later sharded calls create new ones."""
     while _inflight:
         _inflight.popleft().settle()
-    for comm in _scalar_comms.values():
+    for comm, _ in _scalar_comms.values():
         if comm is not None:
             comm.close()
     _scalar_comms.clear()
