@@ -109,3 +109,21 @@ def test_packed_lengths_that_overrun_the_tensor_touch_nothing_beyond_it(W):
         torch.cuda.synchronize()
         assert short.grad.shape == short.shape
         assert torch.isfinite(short.grad).all()
+
+
+@pytest.mark.parametrize("N", [1, 2, 31, 32, 33, 1000, 1024, 1025, 5000, 65535])
+def test_packed_row_offsets_match_a_cumulative_sum(W, N):
+    """ctct_b200_packed_offsets: cu[n] = sum over m < n of min(lx, T) * (min(ly, U) + 1), cu[N] = all rows; the
+    batch sizes straddle the warp and block widths of its scan."""
+    from warp_ctct_b200 import _lib
+    rng = np.random.default_rng(N)
+    T, U1 = 300, 40
+    lx = rng.integers(-3, 400, N).astype(np.int32)       # also values the kernel has to clamp
+    ly = rng.integers(-2, 60, N).astype(np.int32)
+    lx_t, ly_t = _dev(lx, ly)
+    cu = torch.full((N + 1,), -1, dtype=torch.int64, device=DEV)
+    _lib.check(_lib.lib().ctct_b200_packed_offsets(lx_t.data_ptr(), ly_t.data_ptr(), N, T, U1, cu.data_ptr(),
+                                                   _lib.stream_ptr(cu.device)), "packed_offsets")
+    rows = np.clip(lx, 0, T).astype(np.int64) * (np.clip(ly, 0, U1 - 1).astype(np.int64) + 1)
+    want = np.concatenate([[0], np.cumsum(rows)])
+    assert np.array_equal(cu.cpu().numpy(), want)

@@ -219,30 +219,43 @@ struct DenseArgs {
 };
 
 // Row offsets of the packed layout: cu[n] = sum_{m<n} lx[m] * (ly[m] + 1), cu[N] = total rows.
-// One block; N <= 65535.
+// One block; N <= 65535.  Every thread sums a run of utterances, the 1024 run totals are scanned with
+// shuffles (inside the warps, then over the 32 warp totals), and every thread writes its run.
 __global__ void __launch_bounds__(1024) k_packed_offsets(const int *__restrict__ lx, const int *__restrict__ ly, int N, int T,
                                                          int U1, int64_t *__restrict__ cu) {
-    __shared__ long long part[1024];
+    __shared__ long long warp_total[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int per = (N + 1023) / 1024;
     const int lo = threadIdx.x * per, hi = min(N, lo + per);
+    auto rows_of = [&](int n) {
+        return static_cast<long long>(max(0, min(lx[n], T))) * (max(0, min(ly[n], U1 - 1)) + 1);
+    };
     long long s = 0;
-    for (int n = lo; n < hi; ++n) s += static_cast<long long>(max(0, min(lx[n], T))) * (max(0, min(ly[n], U1 - 1)) + 1);
-    part[threadIdx.x] = s;
+    for (int n = lo; n < hi; ++n) s += rows_of(n);
+    long long incl = s;  // inclusive scan of the run totals inside the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const long long v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) warp_total[warp] = incl;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        long long run = 0;
-        for (int i = 0; i < 1024; ++i) {
-            const long long v = part[i];
-            part[i] = run;
-            run += v;
+    if (warp == 0) {  // exclusive scan of the warp totals; lane 31 ends up with the grand total
+        const long long w = warp_total[lane];
+        long long wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long v = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += v;
         }
-        cu[N] = run;
+        warp_total[lane] = wi - w;
+        if (lane == 31) cu[N] = wi;
     }
     __syncthreads();
-    long long run = part[threadIdx.x];
+    long long run = warp_total[warp] + incl - s;
     for (int n = lo; n < hi; ++n) {
         cu[n] = run;
-        run += static_cast<long long>(max(0, min(lx[n], T))) * (max(0, min(ly[n], U1 - 1)) + 1);
+        run += rows_of(n);
     }
 }
 
