@@ -87,8 +87,8 @@ class PendingLoss(torch.Tensor):
             return func(*args, **(kwargs or {}))
 
 
-# Collectives in flight whose buffers must stay alive until the communication stream is done with
-# them.  A finished one is dropped after a look at its state from the host (no operation goes into the
+# Collectives in flight, as (handle, alias of the buffer): the buffers must stay alive until the
+# communication stream is done with them.  A finished one is dropped after a look at its state from the host (no operation goes into the
 # compute stream: a wait or a record between two kernels of the loss costs their programmatic overlap,
 # a few microseconds each).  The host may run a few hundred kernels ahead of the GPU, so "still running"
 # is the normal state of the newest entries; only when _MAX_INFLIGHT of them are, is the oldest one
@@ -239,7 +239,7 @@ def close_scalar_comms() -> None:
     """Destroys the communicators this module created (every rank calls it, before
     torch.distributed.destroy_process_group); later sharded calls create new ones."""
     while _inflight:
-        _inflight.popleft().settle()
+        _inflight.popleft()[0].wait()
     for comm, _ in _scalar_comms.values():
         if comm is not None:
             comm.close()
@@ -269,14 +269,15 @@ def _pending(out: torch.Tensor, handle) -> torch.Tensor:
     PendingLoss that owns the handle; enters it into the queue of collectives in flight."""
     if handle is None:
         return out
+    queue = _inflight
+    while queue and queue[0][0].is_completed():
+        queue.popleft()
+    # a detached alias keeps the storage alive without holding on to the autograd graph (and what it saved)
+    queue.append((handle, out.detach()))
+    while len(queue) > _MAX_INFLIGHT:
+        queue.popleft()[0].wait()
     res = out.as_subclass(PendingLoss)
     res._work = handle
-    queue = _inflight
-    while queue and (queue[0]._work is None or queue[0]._work.is_completed()):
-        queue.popleft()
-    queue.append(res)   # shares its storage with the buffer: keeps it alive
-    while len(queue) > _MAX_INFLIGHT:
-        queue.popleft().settle()
     return res
 
 
