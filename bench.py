@@ -13,7 +13,8 @@ With N > 1 (launched by torchrun, one rank per GPU) the global batch is split le
 ranks; the only collective is the 4-byte all-reduce of the scalar loss.  ``--scaling weak`` (default)
 keeps 32 utterances per GPU; ``--scaling strong`` keeps the global batch at 256 (32 per GPU at N=8).
 
-Timing: W >= 3 warm-up steps, then R passes (default 5) of exactly K steps, each pass bracketed by a
+Timing: W >= 3 warm-up steps plus more until 0.3 s have gone by (``warmup`` of the line is the number of
+untimed steps actually run), then R passes (default 5) of exactly K steps, each pass bracketed by a
 barrier + synchronize and timed with CUDA events, max over ranks; ``ms_per_step`` is the median pass,
 the others are listed under ``passes``.  Inputs and outputs are far larger than L2.
 
@@ -370,6 +371,30 @@ class Timer:
         return per, statistics.median(host), out
 
 
+def settle(step, warmup, world, seconds=0.3):
+    """The W warm-up steps, then more of them until `seconds` of wall time have gone by: with several ranks per
+    box the first tenth of a second of a run is slower than the rest (the first two passes of 40 ms each took 0.25
+    instead of 0.21 ms per step at 8 GPUs), and the timed passes should not start inside it.  The ranks go on in
+    rounds of 50 steps and agree after each round whether to stop, so that all run the same number of steps.
+    Returns the number of untimed steps."""
+    import torch
+    for _ in range(warmup):
+        step()
+    extra, t0 = 0, time.perf_counter()
+    while True:
+        for _ in range(50):
+            step()
+        extra += 50
+        stop = time.perf_counter() - t0 >= seconds
+        if world > 1:
+            import torch.distributed as dist
+            flag = torch.tensor([1 if stop else 0], dtype=torch.int32, device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            stop = bool(flag.item())
+        if stop:
+            return warmup + extra
+
+
 def pass_stats(per):
     med = statistics.median(per)
     return {"n": len(per), "ms_per_step": [round(p, 6) for p in per], "median": med, "min": min(per), "max": max(per),
@@ -442,8 +467,7 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
         loss.backward()
         return loss
 
-    for _ in range(max(args.warmup, 3)):
-        step()
+    warm = settle(step, max(args.warmup, 3), world)
     timer.barrier()
 
     sampler = ClockSampler(local_rank) if (rank == 0 and primary) else None
@@ -453,7 +477,7 @@ def measure_standard(args, name, world, rank, local_rank, dev, timer, primary=Tr
     clocks = sampler.finish() if sampler else None
     ms_step = statistics.median(per)
     loss_value = float(loss.item())
-    res = {"value": G / (ms_step * 1e-3), "ms_per_step": ms_step, "passes": pass_stats(per), "steps": steps,
+    res = {"value": G / (ms_step * 1e-3), "ms_per_step": ms_step, "passes": pass_stats(per), "steps": steps, "warmup_steps": warm,
            "global_batch": G, "clocks": clocks, "host_enqueue_us_per_step": host_us, "loss": loss_value}
 
     # the same K steps once more with the library recording CUDA events around its kernels (the event
@@ -689,7 +713,7 @@ def run_b200(args):
     launches_per_step = 4
     line = {
         "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+        "warmup": res["warmup_steps"], "ms_per_step": res["ms_per_step"], "higher_is_better": True,
         "scaling": args.scaling, "vs_baseline": None, "dtype": dt, "data": "synthetic",
         "config": make_config(name, world, args.scaling),
         "clocks": res["clocks"], "e2e": res["e2e"], "gpu_launches": launches_per_step * args.steps * args.passes * world,
@@ -888,8 +912,7 @@ def run_b200_simple(args):
         loss.backward()
         return loss
 
-    for _ in range(max(args.warmup, 3)):
-        step()
+    warm = settle(step, max(args.warmup, 3), world)
     timer.barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
@@ -1017,7 +1040,7 @@ def run_b200_simple(args):
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": make_config(name, world, args.scaling),
         "clocks": clocks, "e2e": e2e, "gpu_launches": (12 if U1 <= 128 else 13) * args.steps * args.passes * world,
