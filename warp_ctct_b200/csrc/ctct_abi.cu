@@ -1358,6 +1358,15 @@ static int simple_backward_impl(const float *grads3, const float *grad_out, cons
     p.T = (int)T;
     p.U1 = (int)U1;
     p.V = (int)V;
+    if (grad_f && grad_g && T > 0) {  // both: one launch, side by side
+        const int g_blocks = (int)((U1 + 31) / 32);
+        dim3 grid((unsigned)(g_blocks + (T + 7) / 8), (unsigned)N);
+        launch_pdl(k_simple_patch_fg, grid, dim3(256), 0, st, p, g_blocks);
+        int rc = check_launch("simple_patch_fg");
+        if (rc) return rc;
+        prof_mark(slot, 3, st);
+        return CTCT_OK;
+    }
     if (grad_f && T > 0) {
         dim3 grid((unsigned)((T + 7) / 8), (unsigned)N);  // one warp per frame
         launch_pdl(k_simple_patch_f, grid, dim3(256), 0, st, p);

@@ -272,11 +272,10 @@ struct PatchArgs {
 // grad_f[n,t,0] += sum_u g0;  grad_f[n,t,ys[j]] += g2[t,j] + g1[t,j+1].  One warp per (n,t): the
 // blank column gets the warp's sum in one add instead of one atomic per context on the same
 // address; labels may repeat inside an utterance, hence atomics for the label columns.
-__global__ void __launch_bounds__(256) k_simple_patch_f(const PatchArgs a) {
-    pdl_wait();
+__device__ __forceinline__ void simple_patch_f_block(const PatchArgs &a, const int bx) {
     const int n = blockIdx.y;
     const int U = a.U1 - 1;
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int t = bx * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     const int Tn = max(0, min(a.lx[n], a.T)), Un = max(0, min(a.ly[n], U));
     if (t >= Tn) return;
@@ -299,18 +298,22 @@ __global__ void __launch_bounds__(256) k_simple_patch_f(const PatchArgs a) {
     if (lane == 0) atomicAdd(row, sc * blank);  // a label equal to the blank index lands here too
 }
 
+__global__ void __launch_bounds__(256) k_simple_patch_f(const PatchArgs a) {
+    pdl_wait();
+    simple_patch_f_block(a, blockIdx.x);
+}
+
 // grad_g[n,u,{0, ys[u-1], ys[u]}] += sum_t of the three slots.  One block per (utterance, 32 contexts):
 // lanes run along u, so that a warp reads 512 contiguous bytes of records per frame, the 8 warps
 // take the frames round-robin, and their partial sums meet in shared memory (fixed order).
-__global__ void __launch_bounds__(256) k_simple_patch_g(const PatchArgs a, int N) {
+__device__ __forceinline__ void simple_patch_g_block(const PatchArgs &a, const int bx) {
     __shared__ float part[8][32][3];
-    pdl_wait();
     const int n = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int u = blockIdx.x * 32 + lane;
+    const int u = bx * 32 + lane;
     const int U = a.U1 - 1;
     const int Tn = max(0, min(a.lx[n], a.T)), Un = max(0, min(a.ly[n], U));
-    if (blockIdx.x * 32 > Un) return;
+    if (bx * 32 > Un) return;
     float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f;
     if (u <= Un) {
         const float4 *g3 = a.grads3 + static_cast<int64_t>(n) * a.T * a.U1 + u;
@@ -350,7 +353,23 @@ __global__ void __launch_bounds__(256) k_simple_patch_g(const PatchArgs a, int N
         if (u >= 1) row[min(max(a.ys[static_cast<int64_t>(n) * U + u - 1], 0), a.V - 1)] += sc * s1;
         if (u < Un) row[min(max(a.ys[static_cast<int64_t>(n) * U + u], 0), a.V - 1)] += sc * s2;
     }
+}
+
+__global__ void __launch_bounds__(256) k_simple_patch_g(const PatchArgs a, int N) {
+    pdl_wait();
+    simple_patch_g_block(a, blockIdx.x);
     (void)N;
+}
+
+// Both label patches in one launch: they write different tensors and need nothing of each other.  The first
+// `g_blocks` blocks of a row of the grid take the (longer) sums over the frames for grad_g, the others the frames of
+// grad_f, so that the two run side by side instead of one behind the other.
+__global__ void __launch_bounds__(256) k_simple_patch_fg(const PatchArgs a, int g_blocks) {
+    pdl_wait();
+    if (static_cast<int>(blockIdx.x) < g_blocks)
+        simple_patch_g_block(a, blockIdx.x);
+    else
+        simple_patch_f_block(a, blockIdx.x - g_blocks);
 }
 
 // ---------------------------------------------------------------------------------------
